@@ -354,6 +354,9 @@ int pa_layer_norm_f32(const float* d_x, const float* d_gamma, const float* d_bet
 size_t pa_linear_workspace_bytes(int rows, int K, int N);
 int pa_linear_f32(const float* d_x, const float* d_W, const float* d_bias, int rows, int K, int N,
                   int act, float* d_out, void* d_workspace, size_t workspace_bytes, pa_stream_t stream);
+/* pa_linear_f32 restricted to the fp32 FMA kernels whatever the size: products and sums in IEEE float. */
+int pa_linear_f32_exact(const float* d_x, const float* d_W, const float* d_bias, int rows, int K, int N,
+                        int act, float* d_out, void* d_workspace, size_t workspace_bytes, pa_stream_t stream);
 /* The same layer on weights repacked ONCE (at load) into the tensor-core kernel's own order:
  * [ceil(N/128) feature tiles][ceil(K/32) K blocks][32 k][128 n] f32, zero padded, so that every block the
  * kernel streams is one contiguous 16 KB run (whole DRAM pages instead of 512-byte rows 4*N bytes apart).
@@ -530,6 +533,91 @@ size_t pa_nccl_gather_bytes(int world, int rows, int head_dim);
 int pa_nccl_allgather_combine(void* comm, int world, const float* d_part_m, const float* d_part_l,
                               const float* d_part_o, int rows, int head_dim, void* d_gather_ws,
                               size_t gather_bytes, float* d_out, float* d_lse_out, pa_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Ragged-batch sequence ops (no counterpart in the reference: decoder stacks with a float residual stream,
+ * per-sequence recurrent state and routed experts).  A step's rows are the concatenated PORTIONS of several
+ * sequences (prompt chunks and single decoded tokens).  `elem` is the activation element size: 4 = float,
+ * 2 = bfloat16; norms, recurrences, softmax and the residual are float either way.
+ * ------------------------------------------------------------------------------------------------------------ */
+/* x[r] = table[ids[r]] (table in the activation type) as float; out-of-range ids give zeros. */
+int pa_embedding_rows(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
+                      float* d_out, pa_stream_t stream);
+/* RMS norm h = x / sqrt(mean(x^2) + eps) * g with g = d_gain_vec[j] (per channel) or the scalar `gain`
+ * (d_gain_vec NULL), written to d_out (may be NULL).  With d_shift and d_out_shifted: token shift
+ * hs = h + (h' - h) * shift[j], h' = the normalised row d_row_prev[r] of this batch, or, for d_row_prev[r] < 0,
+ * the row d_state[d_row_slot[r]] (the previous portion's last h; zeros for a new sequence). */
+int pa_rms_norm_shift(const float* d_x, int rows, int width, float eps, float gain, const float* d_gain_vec,
+                      const float* d_shift, const int32_t* d_row_prev, const int32_t* d_row_slot,
+                      const float* d_state, void* d_out, void* d_out_shifted, int elem, pa_stream_t stream);
+/* d_state[slot of portion s] = normalised last row of portion s (call after pa_rms_norm_shift of the same x). */
+int pa_rms_norm_state_store(const float* d_x, int width, float eps, float gain, const float* d_gain_vec,
+                            const int32_t* d_seq_start, const int32_t* d_seq_len, const int32_t* d_seq_slot,
+                            int num_seqs, float* d_state, pa_stream_t stream);
+/* minGRU over every portion: rows of d_zxg are [z | u | g] pre-activations (3 * width);
+ * z = sigmoid(z + z_bias), c = u + x_bias >= 0 ? . + 1/2 : sigmoid(.), S = (1 - z) S + z c from d_state[slot],
+ * y = S * silu(g); d_state[slot] is left at the portion's last S.  _chunked: the same result (up to float
+ * rounding) as a three-pass scan over host-listed chunks, for long portions. */
+int pa_mingru_scan(const void* d_zxg, const float* d_z_bias, const float* d_x_bias, int width,
+                   const int32_t* d_seq_start, const int32_t* d_seq_len, const int32_t* d_seq_slot, int num_seqs,
+                   float* d_state, void* d_y, int elem, pa_stream_t stream);
+size_t pa_mingru_chunked_workspace_bytes(int num_chunks, int width);
+int pa_mingru_scan_chunked(const void* d_zxg, const float* d_z_bias, const float* d_x_bias, int width,
+                           const int32_t* d_chunk_start, const int32_t* d_chunk_len, int num_chunks,
+                           const int32_t* d_seq_chunk0, const int32_t* d_seq_nchunks, const int32_t* d_seq_slot,
+                           int num_seqs, float* d_state, void* d_y, int elem, void* d_workspace,
+                           size_t workspace_bytes, pa_stream_t stream);
+/* x = gelu_erf(x) in place; out[r, j] = silu(gu[r, j]) * gu[r, ff + j]. */
+int pa_gelu_inplace(void* d_x, int64_t n, int elem, pa_stream_t stream);
+int pa_silu_mul(const void* d_gate_up, int64_t rows, int ff, void* d_out, int elem, pa_stream_t stream);
+/* x += mult * (mix + dense + sum_k routed[r * top + k] + shared_gate[r] * shared); every term optional. */
+int pa_residual_combine(float* d_x, int64_t rows, int width, float mult, const void* d_mix, const void* d_dense,
+                        const float* d_routed, int top, const void* d_shared, const float* d_shared_gate,
+                        int elem, pa_stream_t stream);
+int pa_gather_rows_f32(const float* d_src, const int32_t* d_rows, int n, int width, float* d_dst,
+                       pa_stream_t stream);
+
+/* K/V rows of a projection buffer -> page pools with separate key and value widths (K pages
+ * [total_pages][tile_size][k_dim], V pages [..][v_dim]); row r goes to position d_row_pos[r] of table row
+ * d_row_slot[r]; the key of kv head g starts at column k_off + g * k_dim of the source row. */
+int pa_kv_append_rows(void* d_k_pool, void* d_v_pool, const int32_t* d_table, int num_slots, int num_kv_heads,
+                      int num_tiles, int total_pages, int tile_size, int k_dim, int v_dim, const void* d_src,
+                      int64_t src_stride, int k_off, int v_off, const int32_t* d_row_slot,
+                      const int32_t* d_row_pos, int rows, int elem, pa_stream_t stream);
+/* Differential attention (two softmax maps per head over one value tensor, out = headwise_rms(a1 - lambda a2) *
+ * out_mult) with a position-dependent query temperature 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1),
+ * causal, over the paged pools.  d_q_tiles [num_q_tiles][4] = (first row, tokens, slot, first position): runs of
+ * at most pa_diff_attention_tile_tokens(heads, kv_heads) consecutive tokens of one portion.  nsplit > 1 cuts
+ * the keys of every tile into that many parts (workspace: pa_diff_attention_workspace_bytes). */
+int pa_diff_attention_tile_tokens(int heads, int kv_heads);
+size_t pa_diff_attention_workspace_bytes(int num_q_tiles, int heads, int kv_heads, int vdim, int nsplit);
+int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
+                      const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
+                      int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
+                      float scale, float temp_coef, int temp_every, float lambda, float out_mult, float eps,
+                      void* d_out, int elem, int nsplit, void* d_workspace, size_t workspace_bytes,
+                      pa_stream_t stream);
+
+/* Router: float logits h . w_router[e], score_fn 0 = sigmoid / 1 = softmax, the `top` largest (ties: lower id),
+ * optionally renormalised; d_w_shared_gate (optional): shared_gate[r] = sigmoid(h . w). */
+int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_w_shared_gate, int rows, int width,
+                   int experts, int top, int score_fn, int renorm, int32_t* d_sel_id, float* d_sel_w,
+                   float* d_shared_gate, int elem, pa_stream_t stream);
+/* Group the rows * top (row, choice) pairs by expert: d_order [pairs], d_meta [pa_moe_meta_ints] (offsets and
+ * the row tiles of the grouped products). */
+int pa_moe_tile_rows(void);
+int pa_moe_max_tiles(int pairs, int experts);
+size_t pa_moe_meta_ints(int pairs, int experts);
+int pa_moe_sort(const int32_t* d_sel_id, int pairs, int experts, int32_t* d_order, int32_t* d_meta,
+                pa_stream_t stream);
+/* act[i] = silu(W_gate[e] a) * (W_up[e] a), a = h[row(i)] * sel_w (input scaling; d_sel_w NULL: none), weights
+ * [experts][2 * ff][width] (gate rows, then up rows); sorted pair order. */
+int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up, int width, int ff, int experts,
+                   const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs,
+                   void* d_act, int elem, pa_stream_t stream);
+/* out_pairs[row * top + choice] = W_down[e] act[i] as float, weights [experts][width][ff]. */
+int pa_moe_down(const void* d_act, const void* d_w_down, int ff, int width, int experts, const int32_t* d_order,
+                const int32_t* d_meta, int pairs, float* d_out_pairs, int elem, pa_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -574,15 +574,15 @@ PA_API size_t pa_linear_workspace_bytes(int rows, int K, int N) {
 
 // The K-slice partials live in the CALLER's workspace (no library-owned scratch: a pointer captured in a CUDA
 // graph stays valid, streams never share it).  Without a large enough workspace the layer runs unsliced.
-PA_API int pa_linear_f32(const float* d_x, const float* d_W, const float* d_bias, int rows, int K, int N, int act,
-                         float* d_out, void* d_workspace, size_t workspace_bytes, pa_stream_t stream) {
+static int linear_f32_impl(const float* d_x, const float* d_W, const float* d_bias, int rows, int K, int N, int act,
+                           float* d_out, void* d_workspace, size_t workspace_bytes, pa_stream_t stream, bool allow_tc) {
     PA_CHECK_ARG(d_x && d_W && d_out && rows >= 0 && K > 0 && N > 0);
     PA_CHECK_ARG(act == PA_ACT_NONE || act == PA_ACT_RELU);
     PA_CHECK_ARG(d_x != d_out);
     if (rows == 0) return PA_OK;
     const DeviceInfo& di = device_info();
     if (!di.ok) return PA_ERR_NO_DEVICE;
-    if (linear_uses_tc(d_x, d_W, d_out, d_bias, rows, K, N))
+    if (allow_tc && linear_uses_tc(d_x, d_W, d_out, d_bias, rows, K, N))
         return pa_linear_tc_run(d_x, d_W, d_bias, rows, K, N, act, d_out, d_workspace, workspace_bytes, 0, di.sm_count,
                                 as_stream(stream));
     const bool gemm = linear_uses_gemm(d_x, d_W, d_out, d_bias, rows, K, N);
@@ -623,6 +623,18 @@ PA_API int pa_linear_f32(const float* d_x, const float* d_W, const float* d_bias
                                                                                         nslices, act, d_out);
     }
     PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_linear_f32(const float* d_x, const float* d_W, const float* d_bias, int rows, int K, int N, int act,
+                         float* d_out, void* d_workspace, size_t workspace_bytes, pa_stream_t stream) {
+    return linear_f32_impl(d_x, d_W, d_bias, rows, K, N, act, d_out, d_workspace, workspace_bytes, stream, true);
+}
+
+// The same layer with every product and sum in IEEE float (the SIMT kernels only, whatever the size): for callers
+// whose contract is 32-bit arithmetic proper rather than fp32-class accuracy.
+PA_API int pa_linear_f32_exact(const float* d_x, const float* d_W, const float* d_bias, int rows, int K, int N, int act,
+                               float* d_out, void* d_workspace, size_t workspace_bytes, pa_stream_t stream) {
+    return linear_f32_impl(d_x, d_W, d_bias, rows, K, N, act, d_out, d_workspace, workspace_bytes, stream, false);
 }
 
 // ---- packed weights: the tensor-core kernel's own layout (every tile's K block one contiguous 16 KB run) ----

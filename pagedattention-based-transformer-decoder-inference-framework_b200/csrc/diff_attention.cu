@@ -1,0 +1,373 @@
+// diff_attention.cu -- differential softmax attention over the paged KV pools for a RAGGED batch (prompt portions and
+// single decoded tokens in one launch), plus the append that feeds it.
+//
+// Per query head two attention maps share one value tensor: the query row holds [map 1 | map 2] (2 * dim values), so
+// does the key row of its key/value head; out = rmsnorm_headwise(a1 - lambda * a2) * out_mult, where a_i =
+// softmax_i(q_i . k_i * scale) V over the causally visible keys.  The query is first multiplied by a position-dependent
+// temperature 1 + coef * ln(floor((p + 1) / every) + 1).  Scores, softmax weights, both weighted sums, the difference
+// and the head-wise norm are float; K/V pages are stored in the activation type (float or bfloat16).
+//
+// Pools: K pages [total_pages][tile_size][2 * dim], V pages [total_pages][tile_size][vdim]; a (slot, kv head, tile)
+// entry of the page table names the page of both.  Unmapped pages are skipped, as in the decode kernels.
+//
+// Work unit: a CTA of 8 warps owns 32 (token, head) rows that read the SAME key/value head: up to 32 / hc consecutive
+// tokens of one portion x hc = min(32, heads per kv head) query heads, so every K/V byte staged in shared memory serves
+// all of them.  Keys are staged 32 at a time (one key per lane for the scores; lanes switch to value columns for the
+// weighted sums).  Long contexts with few CTAs are cut along the keys into `nsplit` parts whose (m, l, acc) partials a
+// second kernel merges before the difference and the norm are taken.
+#include "seq_common.cuh"
+
+namespace pa {
+
+constexpr int kDaRows = 32;     // (token, head) rows per CTA
+constexpr int kDaWarps = 8;
+constexpr int kDaRpw = kDaRows / kDaWarps;
+constexpr int kDaKeys = 32;     // keys staged per step
+
+struct DiffAttnParams {
+    const void* q;              // rows of the projection buffer; the query of head h starts at q_off + h * 2 * dim
+    int64_t q_stride;
+    int q_off;
+    const void* k_pool;
+    const void* v_pool;
+    const int32_t* table;
+    int num_slots, num_kv_heads, num_tiles, total_pages, tile_size;
+    const int32_t* tiles;       // [ntiles][4]: first row, tokens, slot, position of the first token
+    int heads, dim, vdim;
+    float scale, temp_coef;
+    int temp_every;
+    float lambda, out_mult, eps;
+    void* out;                  // [rows][heads * vdim]
+    int nsplit;
+    float* partial;             // nsplit > 1: [(tile, y, split, row)][4 + 2 * vdim]
+};
+
+__device__ __forceinline__ void da_geometry(int heads, int kv_heads, int& hpg, int& hc, int& nchunk) {
+    hpg = heads / kv_heads;
+    hc = hpg < kDaRows ? hpg : kDaRows;
+    nchunk = (hpg + hc - 1) / hc;
+}
+
+template <typename T>
+__global__ void kv_append_rows_kernel(T* __restrict__ k_pool, T* __restrict__ v_pool, const int32_t* __restrict__ table,
+                                      int num_slots, int num_kv_heads, int num_tiles, int total_pages, int tile_size,
+                                      int k_dim, int v_dim, const T* __restrict__ src, int64_t src_stride, int k_off,
+                                      int v_off, const int32_t* __restrict__ row_slot,
+                                      const int32_t* __restrict__ row_pos, int rows) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (w >= (int64_t)rows * num_kv_heads) return;
+    const int g = (int)(w % num_kv_heads);
+    const int r = (int)(w / num_kv_heads);
+    const int slot = row_slot[r], pos = row_pos[r];
+    if (pos < 0 || pos / tile_size >= num_tiles || (unsigned)slot >= (unsigned)num_slots) return;
+    const int page = table[((int64_t)slot * num_kv_heads + g) * num_tiles + pos / tile_size];
+    if (page < 0 || page >= total_pages) return;
+    const int64_t prow = (int64_t)page * tile_size + pos % tile_size;
+    const T* sk = src + (int64_t)r * src_stride + k_off + (int64_t)g * k_dim;
+    const T* sv = src + (int64_t)r * src_stride + v_off + (int64_t)g * v_dim;
+    for (int d = lane; d < k_dim; d += 32) k_pool[prow * k_dim + d] = sk[d];
+    for (int d = lane; d < v_dim; d += 32) v_pool[prow * v_dim + d] = sv[d];
+}
+
+// Difference of the two maps, head-wise RMS norm and the output factor for one row held across a warp
+// (value column lane + 32 i in slot i).
+template <typename T, int NV>
+__device__ __forceinline__ void da_finish_row(const float (&a1)[NV], const float (&a2)[NV], float l1, float l2,
+                                              const DiffAttnParams& p, int lane, T* __restrict__ dst) {
+    float o[NV];
+    float ss = 0.f;
+    const float i1 = 1.0f / l1, i2 = 1.0f / l2;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const bool ok = lane + 32 * i < p.vdim;
+        o[i] = ok ? a1[i] * i1 - p.lambda * (a2[i] * i2) : 0.f;
+        ss = fmaf(o[i], o[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float rn = 1.0f / sqrtf(ss / (float)p.vdim + p.eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (lane + 32 * i < p.vdim) dst[lane + 32 * i] = from_f32<T>(o[i] * rn * p.out_mult);
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kDaWarps * 32) diff_attention_kernel(const DiffAttnParams p) {
+    extern __shared__ float smem[];
+    const int kd = 2 * p.dim, kds = kd + 1;
+    float* Qs = smem;                              // [32][kd]
+    float* Ks = Qs + kDaRows * kd;                 // [32][kd + 1]
+    float* Vs = Ks + kDaKeys * kds;                // [32][vdim]
+    __shared__ int64_t page_row[kDaKeys];          // first pool row of the staged key's page entry, or -1
+
+    int hpg, hc, nchunk;
+    da_geometry(p.heads, p.num_kv_heads, hpg, hc, nchunk);
+    const int bq = kDaRows / hc;
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], ntok = tile[1], slot = tile[2], pos0 = tile[3];
+    const int g = blockIdx.y / nchunk, chunk = blockIdx.y % nchunk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* kp = static_cast<const T*>(p.k_pool);
+    const T* vp = static_cast<const T*>(p.v_pool);
+
+    // ---- queries: temperature applied in float
+    for (int idx = threadIdx.x; idx < kDaRows * kd; idx += blockDim.x) {
+        const int r = idx / kd, d = idx % kd;
+        const int tok = r / hc, hh = chunk * hc + r % hc;
+        float v = 0.f;
+        if (tok < bq && tok < ntok && hh < hpg) {
+            const int pos = pos0 + tok;
+            const float temp = 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f);
+            const T* qr = static_cast<const T*>(p.q) + (int64_t)(row0 + tok) * p.q_stride + p.q_off +
+                          (int64_t)(g * hpg + hh) * kd;
+            v = to_f32<T>(qr[d]) * temp;
+        }
+        Qs[idx] = v;
+    }
+
+    int rpos[kDaRpw];       // last visible key of the row, -1 for an unused row
+    float m1[kDaRpw], l1[kDaRpw], m2[kDaRpw], l2[kDaRpw];
+    float a1[kDaRpw][NV], a2[kDaRpw][NV];
+#pragma unroll
+    for (int r = 0; r < kDaRpw; ++r) {
+        const int row = warp * kDaRpw + r;
+        const int tok = row / hc, hh = chunk * hc + row % hc;
+        rpos[r] = (tok < bq && tok < ntok && hh < hpg) ? pos0 + tok : -1;
+        m1[r] = m2[r] = -INFINITY;
+        l1[r] = l2[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) a1[r][i] = a2[r][i] = 0.f;
+    }
+
+    const int total = pos0 + ntok;                       // keys any row of the tile may see
+    const int nsteps = (total + kDaKeys - 1) / kDaKeys;
+    const int per = (nsteps + p.nsplit - 1) / p.nsplit;
+    const int s_begin = blockIdx.z * per, s_end = min(nsteps, s_begin + per);
+
+    for (int st = s_begin; st < s_end; ++st) {
+        const int c0 = st * kDaKeys;
+        __syncthreads();                                 // the previous step's tiles are consumed (and Qs is written)
+        if (threadIdx.x < kDaKeys) {
+            const int j = c0 + threadIdx.x;
+            int64_t pr = -1;
+            if (j < total && j / p.tile_size < p.num_tiles) {
+                const int page = p.table[((int64_t)slot * p.num_kv_heads + g) * p.num_tiles + j / p.tile_size];
+                if (page >= 0 && page < p.total_pages) pr = (int64_t)page * p.tile_size + j % p.tile_size;
+            }
+            page_row[threadIdx.x] = pr;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kDaKeys * kd; idx += blockDim.x) {
+            const int key = idx / kd, d = idx % kd;
+            const int64_t pr = page_row[key];
+            Ks[key * kds + d] = pr >= 0 ? to_f32<T>(kp[pr * kd + d]) : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < kDaKeys * p.vdim; idx += blockDim.x) {
+            const int key = idx / p.vdim, d = idx % p.vdim;
+            const int64_t pr = page_row[key];
+            Vs[idx] = pr >= 0 ? to_f32<T>(vp[pr * p.vdim + d]) : 0.f;
+        }
+        __syncthreads();
+
+        // ---- scores: lane = key
+        float s1[kDaRpw], s2[kDaRpw];
+#pragma unroll
+        for (int r = 0; r < kDaRpw; ++r) s1[r] = s2[r] = 0.f;
+        const float* kr = Ks + lane * kds;
+        const float* qb = Qs + warp * kDaRpw * kd;
+        for (int d = 0; d < p.dim; ++d) {
+            const float k1 = kr[d], k2 = kr[p.dim + d];
+#pragma unroll
+            for (int r = 0; r < kDaRpw; ++r) {
+                s1[r] = fmaf(qb[r * kd + d], k1, s1[r]);
+                s2[r] = fmaf(qb[r * kd + p.dim + d], k2, s2[r]);
+            }
+        }
+        const int j = c0 + lane;
+        const bool mapped = page_row[lane] >= 0;
+        float p1[kDaRpw], p2[kDaRpw];
+#pragma unroll
+        for (int r = 0; r < kDaRpw; ++r) {
+            const bool vis = mapped && j <= rpos[r];
+            const float v1 = vis ? s1[r] * p.scale : -INFINITY, v2 = vis ? s2[r] * p.scale : -INFINITY;
+            const float n1 = fmaxf(m1[r], warp_max(v1)), n2 = fmaxf(m2[r], warp_max(v2));
+            const float c1 = n1 == -INFINITY ? 1.f : expf(m1[r] - n1), c2 = n2 == -INFINITY ? 1.f : expf(m2[r] - n2);
+            p1[r] = vis ? expf(v1 - n1) : 0.f;
+            p2[r] = vis ? expf(v2 - n2) : 0.f;
+            l1[r] = l1[r] * c1 + warp_sum(p1[r]);
+            l2[r] = l2[r] * c2 + warp_sum(p2[r]);
+            m1[r] = n1;
+            m2[r] = n2;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                a1[r][i] *= c1;
+                a2[r][i] *= c2;
+            }
+        }
+        // ---- weighted sums: lane = value column
+        const int nk = min(kDaKeys, total - c0);
+        for (int jj = 0; jj < nk; ++jj) {
+            float v[NV];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < p.vdim ? Vs[jj * p.vdim + lane + 32 * i] : 0.f;
+#pragma unroll
+            for (int r = 0; r < kDaRpw; ++r) {
+                const float w1 = __shfl_sync(0xffffffffu, p1[r], jj), w2 = __shfl_sync(0xffffffffu, p2[r], jj);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    a1[r][i] = fmaf(w1, v[i], a1[r][i]);
+                    a2[r][i] = fmaf(w2, v[i], a2[r][i]);
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < kDaRpw; ++r) {
+        const int row = warp * kDaRpw + r;
+        if (p.nsplit > 1) {
+            float* dst = p.partial + ((((int64_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit + blockIdx.z) * kDaRows + row) *
+                                         (4 + 2 * p.vdim);
+            if (lane == 0) {
+                dst[0] = m1[r]; dst[1] = l1[r]; dst[2] = m2[r]; dst[3] = l2[r];
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (lane + 32 * i < p.vdim) {
+                    dst[4 + lane + 32 * i] = a1[r][i];
+                    dst[4 + p.vdim + lane + 32 * i] = a2[r][i];
+                }
+        } else if (rpos[r] >= 0) {
+            const int tok = row / hc, hh = chunk * hc + row % hc;
+            T* dst = static_cast<T*>(p.out) + (int64_t)(row0 + tok) * p.heads * p.vdim + (int64_t)(g * hpg + hh) * p.vdim;
+            da_finish_row<T, NV>(a1[r], a2[r], l1[r], l2[r], p, lane, dst);
+        }
+    }
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kDaWarps * 32) diff_attention_merge_kernel(const DiffAttnParams p) {
+    int hpg, hc, nchunk;
+    da_geometry(p.heads, p.num_kv_heads, hpg, hc, nchunk);
+    const int bq = kDaRows / hc;
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], ntok = tile[1];
+    const int g = blockIdx.y / nchunk, chunk = blockIdx.y % nchunk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = 0; r < kDaRpw; ++r) {
+        const int row = warp * kDaRpw + r;
+        const int tok = row / hc, hh = chunk * hc + row % hc;
+        if (!(tok < bq && tok < ntok && hh < hpg)) continue;
+        const float* base = p.partial + (((int64_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit * kDaRows + row) * (4 + 2 * p.vdim);
+        const int64_t zs = (int64_t)kDaRows * (4 + 2 * p.vdim);
+        float M1 = -INFINITY, M2 = -INFINITY;
+        for (int z = 0; z < p.nsplit; ++z) {
+            M1 = fmaxf(M1, base[z * zs + 0]);
+            M2 = fmaxf(M2, base[z * zs + 2]);
+        }
+        float l1 = 0.f, l2 = 0.f, a1[NV], a2[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) a1[i] = a2[i] = 0.f;
+        for (int z = 0; z < p.nsplit; ++z) {
+            const float* pz = base + z * zs;
+            const float w1 = pz[0] == -INFINITY ? 0.f : expf(pz[0] - M1), w2 = pz[2] == -INFINITY ? 0.f : expf(pz[2] - M2);
+            l1 = fmaf(w1, pz[1], l1);
+            l2 = fmaf(w2, pz[3], l2);
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (lane + 32 * i < p.vdim) {
+                    a1[i] = fmaf(w1, pz[4 + lane + 32 * i], a1[i]);
+                    a2[i] = fmaf(w2, pz[4 + p.vdim + lane + 32 * i], a2[i]);
+                }
+        }
+        T* dst = static_cast<T*>(p.out) + (int64_t)(row0 + tok) * p.heads * p.vdim + (int64_t)(g * hpg + hh) * p.vdim;
+        da_finish_row<T, NV>(a1, a2, l1, l2, p, lane, dst);
+    }
+}
+
+template <typename T, int NV>
+static int da_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    int hpg = p.heads / p.num_kv_heads;
+    int hc = hpg < kDaRows ? hpg : kDaRows;
+    int nchunk = (hpg + hc - 1) / hc;
+    const size_t smem = ((size_t)kDaRows * 2 * p.dim + (size_t)kDaKeys * (2 * p.dim + 1) + (size_t)kDaKeys * p.vdim) * sizeof(float);
+    if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(diff_attention_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((unsigned)ntiles, (unsigned)(p.num_kv_heads * nchunk), (unsigned)p.nsplit);
+    diff_attention_kernel<T, NV><<<grid, kDaWarps * 32, smem, st>>>(p);
+    if (p.nsplit > 1) {
+        dim3 g2((unsigned)ntiles, (unsigned)(p.num_kv_heads * nchunk));
+        diff_attention_merge_kernel<T, NV><<<g2, kDaWarps * 32, 0, st>>>(p);
+    }
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+template <typename T>
+static int da_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    const int nv = (p.vdim + 31) / 32;
+    switch (nv) {
+        case 1: return da_launch<T, 1>(p, ntiles, st);
+        case 2: return da_launch<T, 2>(p, ntiles, st);
+        case 3: return da_launch<T, 3>(p, ntiles, st);
+        case 4: return da_launch<T, 4>(p, ntiles, st);
+        case 5: case 6: return da_launch<T, 6>(p, ntiles, st);
+        case 7: case 8: return da_launch<T, 8>(p, ntiles, st);
+        default: return PA_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace pa
+
+using namespace pa;
+
+PA_API int pa_kv_append_rows(void* d_k_pool, void* d_v_pool, const int32_t* d_table, int num_slots, int num_kv_heads,
+                             int num_tiles, int total_pages, int tile_size, int k_dim, int v_dim, const void* d_src,
+                             int64_t src_stride, int k_off, int v_off, const int32_t* d_row_slot,
+                             const int32_t* d_row_pos, int rows, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_k_pool && d_v_pool && d_table && d_src && d_row_slot && d_row_pos && rows >= 0);
+    PA_CHECK_ARG(num_slots > 0 && num_kv_heads > 0 && num_tiles > 0 && total_pages > 0 && tile_size > 0 && k_dim > 0 && v_dim > 0);
+    if (rows == 0) return PA_OK;
+    const int64_t threads = (int64_t)rows * num_kv_heads * 32;
+    PA_DISPATCH_ELEM(elem, kv_append_rows_kernel<T><<<(unsigned)((threads + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               static_cast<T*>(d_k_pool), static_cast<T*>(d_v_pool), d_table, num_slots, num_kv_heads,
+                               num_tiles, total_pages, tile_size, k_dim, v_dim, static_cast<const T*>(d_src), src_stride,
+                               k_off, v_off, d_row_slot, d_row_pos, rows));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_diff_attention_tile_tokens(int heads, int kv_heads) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
+    const int hpg = heads / kv_heads;
+    return kDaRows / (hpg < kDaRows ? hpg : kDaRows);
+}
+
+PA_API size_t pa_diff_attention_workspace_bytes(int num_tiles_q, int heads, int kv_heads, int vdim, int nsplit) {
+    if (nsplit <= 1 || num_tiles_q <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
+    const int hpg = heads / kv_heads, hc = hpg < kDaRows ? hpg : kDaRows, nchunk = (hpg + hc - 1) / hc;
+    return (size_t)num_tiles_q * kv_heads * nchunk * nsplit * kDaRows * (4 + 2 * vdim) * sizeof(float);
+}
+
+PA_API int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
+                             const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
+                             int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
+                             float scale, float temp_coef, int temp_every, float lambda, float out_mult, float eps,
+                             void* d_out, int elem, int nsplit, void* d_workspace, size_t workspace_bytes,
+                             pa_stream_t stream) {
+    PA_CHECK_ARG(d_q && d_k_pool && d_v_pool && d_table && d_q_tiles && d_out && num_q_tiles >= 0);
+    PA_CHECK_ARG(num_slots > 0 && num_kv_heads > 0 && num_tiles > 0 && total_pages > 0 && tile_size > 0);
+    PA_CHECK_ARG(heads > 0 && heads % num_kv_heads == 0 && dim > 0 && vdim > 0 && temp_every > 0);
+    if (num_q_tiles == 0) return PA_OK;
+    if (nsplit < 1) nsplit = 1;
+    if (nsplit > 1 && (!d_workspace || workspace_bytes < pa_diff_attention_workspace_bytes(num_q_tiles, heads, num_kv_heads, vdim, nsplit)))
+        return PA_ERR_WORKSPACE;
+    DiffAttnParams p;
+    p.q = d_q; p.q_stride = q_stride; p.q_off = q_off; p.k_pool = d_k_pool; p.v_pool = d_v_pool; p.table = d_table;
+    p.num_slots = num_slots; p.num_kv_heads = num_kv_heads; p.num_tiles = num_tiles; p.total_pages = total_pages;
+    p.tile_size = tile_size; p.tiles = d_q_tiles; p.heads = heads; p.dim = dim; p.vdim = vdim; p.scale = scale;
+    p.temp_coef = temp_coef; p.temp_every = temp_every; p.lambda = lambda; p.out_mult = out_mult; p.eps = eps;
+    p.out = d_out; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace);
+    if (elem == 4) return da_dispatch<float>(p, num_q_tiles, as_stream(stream));
+    if (elem == 2) return da_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
+    return PA_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,350 @@
+// seq_ops.cu -- per-token ops of decoder stacks that keep a float residual stream and per-sequence recurrent state,
+// over a RAGGED batch: the rows of one step are the concatenated portions of several sequences (a portion is a run of
+// consecutive tokens of one sequence: a prompt chunk, or a single decoded token).  A portion is described by
+// (first row, length, state slot); a row by (state slot, position, row of the previous token or -1).
+//
+//   embedding_rows_kernel     x[r] = table[id[r]] as float
+//   rms_shift_kernel          RMS norm (scalar or per-channel gain) + optional token shift against the previous token's
+//                             normalised row (from the batch, or from the sequence's state slot at a portion's start)
+//   rms_state_store_kernel    state slot <- normalised row of a portion's last token
+//   mingru_scan_kernel        minGRU recurrence S_t = (1 - z_t) S_{t-1} + z_t c_t with the output gate, state in float
+//   mingru_chunk_* kernels    the same recurrence for long portions as a three-pass chunked scan
+//   gelu / silu-mul           activations between two matrix products
+//   residual_combine_kernel   x += m * (mixer + dense ff + sum of routed expert rows + gate * shared expert)
+//
+// Norms, the recurrence with its gates, and the residual sum are computed in float whatever the activation type.
+#include "seq_common.cuh"
+
+namespace pa {
+
+template <typename T>
+__global__ void embedding_rows_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids, int rows, int width,
+                                      int vocab, float* __restrict__ out) {
+    const int r = blockIdx.x;
+    const int id = ids[r];
+    const bool ok = id >= 0 && id < vocab;
+    const T* src = table + (int64_t)(ok ? id : 0) * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) out[(int64_t)r * width + j] = ok ? to_f32<T>(src[j]) : 0.f;
+}
+
+__device__ __forceinline__ float row_inv_rms(const float* __restrict__ xr, int width, float eps, float* sm) {
+    float s = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) s = fmaf(xr[j], xr[j], s);
+    s = block_sum(s, sm);
+    return 1.0f / sqrtf(s / (float)width + eps);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rms_shift_kernel(const float* __restrict__ x, int width, float eps, float g_scalar,
+                                                        const float* __restrict__ g_vec, const float* __restrict__ shift,
+                                                        const int32_t* __restrict__ row_prev,
+                                                        const int32_t* __restrict__ row_slot,
+                                                        const float* __restrict__ state, T* __restrict__ out_h,
+                                                        T* __restrict__ out_hs) {
+    __shared__ float sm[32];
+    const int row = blockIdx.x;
+    const float* xr = x + (int64_t)row * width;
+    const float r = row_inv_rms(xr, width, eps, sm);
+    const bool shifted = shift != nullptr && out_hs != nullptr;
+    const int prev = shifted ? row_prev[row] : -1;
+    const float* xp = nullptr;
+    const float* sp = nullptr;
+    float rp = 0.f;
+    if (shifted) {
+        if (prev >= 0) {
+            xp = x + (int64_t)prev * width;
+            rp = row_inv_rms(xp, width, eps, sm);
+        } else {
+            sp = state + (int64_t)row_slot[row] * width;
+        }
+    }
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float g = g_vec ? g_vec[j] : g_scalar;
+        const float h = xr[j] * r * g;
+        if (out_h) out_h[(int64_t)row * width + j] = from_f32<T>(h);
+        if (shifted) {
+            const float hp = xp ? xp[j] * rp * g : sp[j];
+            out_hs[(int64_t)row * width + j] = from_f32<T>(h + (hp - h) * shift[j]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) rms_state_store_kernel(const float* __restrict__ x, int width, float eps,
+                                                              float g_scalar, const float* __restrict__ g_vec,
+                                                              const int32_t* __restrict__ seq_start,
+                                                              const int32_t* __restrict__ seq_len,
+                                                              const int32_t* __restrict__ seq_slot,
+                                                              float* __restrict__ state) {
+    __shared__ float sm[32];
+    const int s = blockIdx.x;
+    if (seq_len[s] <= 0) return;
+    const float* xr = x + (int64_t)(seq_start[s] + seq_len[s] - 1) * width;
+    const float r = row_inv_rms(xr, width, eps, sm);
+    float* dst = state + (int64_t)seq_slot[s] * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = xr[j] * r * (g_vec ? g_vec[j] : g_scalar);
+}
+
+// ---- minGRU ---------------------------------------------------------------------------------------------------------
+// zxg row layout: [z pre-activation | candidate pre-activation | output-gate pre-activation], each `width` wide.
+template <typename T>
+struct MinGruStep {
+    float a, b, gate;
+    __device__ __forceinline__ MinGruStep(const T* __restrict__ row, int width, int c, float zb, float xb) {
+        const float z = sigmoid_f32(to_f32<T>(row[c]) + zb);
+        const float u = to_f32<T>(row[width + c]) + xb;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f32(u);
+        a = 1.0f - z;
+        b = z * cand;
+        gate = silu_f32(to_f32<T>(row[2 * width + c]));
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ zxg, const float* __restrict__ z_bias,
+                                                          const float* __restrict__ x_bias, int width,
+                                                          const int32_t* __restrict__ seq_start,
+                                                          const int32_t* __restrict__ seq_len,
+                                                          const int32_t* __restrict__ seq_slot, float* __restrict__ state,
+                                                          T* __restrict__ y) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = blockIdx.y;
+    if (c >= width) return;
+    const int n = seq_len[s];
+    if (n <= 0) return;
+    const int64_t r0 = seq_start[s];
+    const float zb = z_bias ? z_bias[c] : 0.f, xb = x_bias ? x_bias[c] : 0.f;
+    float* sp = state + (int64_t)seq_slot[s] * width + c;
+    float S = *sp;
+    for (int t = 0; t < n; ++t) {
+        const MinGruStep<T> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
+        S = st.a * S + st.b;
+        y[(r0 + t) * width + c] = from_f32<T>(S * st.gate);
+    }
+    *sp = S;
+}
+
+// Chunked scan for long portions.  A portion is cut into chunks of `chunk` tokens (chunk list built by the host:
+// chunk -> (first row, length, portion, index within portion)).  Pass 1: every (chunk, channel) folds its tokens into
+// the pair (A, B) with S_out = A * S_in + B.  Pass 2: per (portion, channel) the chunk pairs are chained in order from
+// the state slot, leaving each chunk's S_in in place of its A and the new state in the slot.  Pass 3: every chunk
+// replays its tokens from S_in and writes the outputs.
+template <typename T>
+__global__ void __launch_bounds__(128) mingru_chunk_fold_kernel(const T* __restrict__ zxg, const float* __restrict__ z_bias,
+                                                                const float* __restrict__ x_bias, int width,
+                                                                const int32_t* __restrict__ chunk_start,
+                                                                const int32_t* __restrict__ chunk_len,
+                                                                float* __restrict__ AB) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int k = blockIdx.y;
+    if (c >= width) return;
+    const int n = chunk_len[k];
+    const int64_t r0 = chunk_start[k];
+    const float zb = z_bias ? z_bias[c] : 0.f, xb = x_bias ? x_bias[c] : 0.f;
+    float A = 1.f, B = 0.f;
+    for (int t = 0; t < n; ++t) {
+        const MinGruStep<T> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
+        A *= st.a;
+        B = st.a * B + st.b;
+    }
+    AB[((int64_t)k * 2) * width + c] = A;
+    AB[((int64_t)k * 2 + 1) * width + c] = B;
+}
+
+__global__ void __launch_bounds__(128) mingru_chunk_chain_kernel(float* __restrict__ AB, int width,
+                                                                 const int32_t* __restrict__ seq_chunk0,
+                                                                 const int32_t* __restrict__ seq_nchunks,
+                                                                 const int32_t* __restrict__ seq_slot,
+                                                                 float* __restrict__ state) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int s = blockIdx.y;
+    if (c >= width) return;
+    const int n = seq_nchunks[s];
+    if (n <= 0) return;
+    const int k0 = seq_chunk0[s];
+    float* sp = state + (int64_t)seq_slot[s] * width + c;
+    float S = *sp;
+    for (int k = k0; k < k0 + n; ++k) {
+        const float A = AB[((int64_t)k * 2) * width + c], B = AB[((int64_t)k * 2 + 1) * width + c];
+        AB[((int64_t)k * 2) * width + c] = S;  // the chunk's incoming state
+        S = A * S + B;
+    }
+    *sp = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) mingru_chunk_apply_kernel(const T* __restrict__ zxg, const float* __restrict__ z_bias,
+                                                                 const float* __restrict__ x_bias, int width,
+                                                                 const int32_t* __restrict__ chunk_start,
+                                                                 const int32_t* __restrict__ chunk_len,
+                                                                 const float* __restrict__ AB, T* __restrict__ y) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int k = blockIdx.y;
+    if (c >= width) return;
+    const int n = chunk_len[k];
+    const int64_t r0 = chunk_start[k];
+    const float zb = z_bias ? z_bias[c] : 0.f, xb = x_bias ? x_bias[c] : 0.f;
+    float S = AB[((int64_t)k * 2) * width + c];
+    for (int t = 0; t < n; ++t) {
+        const MinGruStep<T> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
+        S = st.a * S + st.b;
+        y[(r0 + t) * width + c] = from_f32<T>(S * st.gate);
+    }
+}
+
+// ---- activations ----------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gelu_kernel(T* __restrict__ x, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = from_f32<T>(gelu_erf_f32(to_f32<T>(x[i])));
+}
+
+// gu rows are [gate (ff) | up (ff)]; out[r, j] = silu(gate_j) * up_j
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, int64_t rows, int ff, T* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * ff) return;
+    const int64_t r = i / ff;
+    const int j = (int)(i % ff);
+    const float g = to_f32<T>(gu[r * 2 * ff + j]), u = to_f32<T>(gu[r * 2 * ff + ff + j]);
+    out[i] = from_f32<T>(silu_f32(g) * u);
+}
+
+template <typename T>
+__global__ void residual_combine_kernel(float* __restrict__ x, int64_t rows, int width, float mult,
+                                        const T* __restrict__ mix, const T* __restrict__ dense,
+                                        const float* __restrict__ routed, int top, const T* __restrict__ shared,
+                                        const float* __restrict__ shared_gate) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * width) return;
+    const int64_t r = i / width;
+    const int j = (int)(i % width);
+    float s = 0.f;
+    if (mix) s += to_f32<T>(mix[i]);
+    if (dense) s += to_f32<T>(dense[i]);
+    if (routed) {
+        float e = 0.f;
+        for (int k = 0; k < top; ++k) e += routed[(r * top + k) * width + j];
+        s += e;
+    }
+    if (shared) s += (shared_gate ? shared_gate[r] : 1.0f) * to_f32<T>(shared[i]);
+    x[i] = x[i] + mult * s;
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int32_t* __restrict__ rows, int n, int width,
+                                   T* __restrict__ dst) {
+    const int r = blockIdx.x;
+    const T* s = src + (int64_t)rows[r] * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[(int64_t)r * width + j] = s[j];
+}
+
+}  // namespace pa
+
+using namespace pa;
+
+PA_API int pa_embedding_rows(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
+                             float* d_out, pa_stream_t stream) {
+    PA_CHECK_ARG(d_table && d_ids && d_out && rows >= 0 && width > 0 && vocab > 0);
+    if (rows == 0) return PA_OK;
+    PA_DISPATCH_ELEM(elem, embedding_rows_kernel<T><<<rows, 256, 0, as_stream(stream)>>>(
+                               static_cast<const T*>(d_table), d_ids, rows, width, vocab, d_out));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_rms_norm_shift(const float* d_x, int rows, int width, float eps, float gain, const float* d_gain_vec,
+                             const float* d_shift, const int32_t* d_row_prev, const int32_t* d_row_slot,
+                             const float* d_state, void* d_out, void* d_out_shifted, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && rows >= 0 && width > 0 && (d_out || d_out_shifted));
+    PA_CHECK_ARG(!(d_shift && d_out_shifted) || (d_row_prev && d_row_slot && d_state));
+    if (rows == 0) return PA_OK;
+    PA_DISPATCH_ELEM(elem, rms_shift_kernel<T><<<rows, 256, 0, as_stream(stream)>>>(
+                               d_x, width, eps, gain, d_gain_vec, d_shift, d_row_prev, d_row_slot, d_state,
+                               static_cast<T*>(d_out), static_cast<T*>(d_out_shifted)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_rms_norm_state_store(const float* d_x, int width, float eps, float gain, const float* d_gain_vec,
+                                   const int32_t* d_seq_start, const int32_t* d_seq_len, const int32_t* d_seq_slot,
+                                   int num_seqs, float* d_state, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && width > 0 && d_seq_start && d_seq_len && d_seq_slot && d_state && num_seqs >= 0);
+    if (num_seqs == 0) return PA_OK;
+    rms_state_store_kernel<<<num_seqs, 256, 0, as_stream(stream)>>>(d_x, width, eps, gain, d_gain_vec, d_seq_start,
+                                                                   d_seq_len, d_seq_slot, d_state);
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_mingru_scan(const void* d_zxg, const float* d_z_bias, const float* d_x_bias, int width,
+                          const int32_t* d_seq_start, const int32_t* d_seq_len, const int32_t* d_seq_slot, int num_seqs,
+                          float* d_state, void* d_y, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_zxg && width > 0 && d_seq_start && d_seq_len && d_seq_slot && d_state && d_y && num_seqs >= 0);
+    if (num_seqs == 0) return PA_OK;
+    dim3 grid((unsigned)((width + 127) / 128), (unsigned)num_seqs);
+    PA_DISPATCH_ELEM(elem, mingru_scan_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
+                               static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_seq_start, d_seq_len,
+                               d_seq_slot, d_state, static_cast<T*>(d_y)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API size_t pa_mingru_chunked_workspace_bytes(int num_chunks, int width) {
+    return num_chunks > 0 && width > 0 ? (size_t)num_chunks * 2 * width * sizeof(float) : 0;
+}
+
+PA_API int pa_mingru_scan_chunked(const void* d_zxg, const float* d_z_bias, const float* d_x_bias, int width,
+                                  const int32_t* d_chunk_start, const int32_t* d_chunk_len, int num_chunks,
+                                  const int32_t* d_seq_chunk0, const int32_t* d_seq_nchunks, const int32_t* d_seq_slot,
+                                  int num_seqs, float* d_state, void* d_y, int elem, void* d_workspace,
+                                  size_t workspace_bytes, pa_stream_t stream) {
+    PA_CHECK_ARG(d_zxg && width > 0 && d_chunk_start && d_chunk_len && d_seq_chunk0 && d_seq_nchunks && d_seq_slot);
+    PA_CHECK_ARG(d_state && d_y && num_seqs >= 0 && num_chunks >= 0);
+    if (num_seqs == 0 || num_chunks == 0) return PA_OK;
+    if (!d_workspace || workspace_bytes < pa_mingru_chunked_workspace_bytes(num_chunks, width)) return PA_ERR_WORKSPACE;
+    float* AB = static_cast<float*>(d_workspace);
+    const unsigned gx = (unsigned)((width + 127) / 128);
+    cudaStream_t st = as_stream(stream);
+    PA_DISPATCH_ELEM(elem, {
+        mingru_chunk_fold_kernel<T><<<dim3(gx, (unsigned)num_chunks), 128, 0, st>>>(
+            static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_chunk_start, d_chunk_len, AB);
+        mingru_chunk_chain_kernel<<<dim3(gx, (unsigned)num_seqs), 128, 0, st>>>(AB, width, d_seq_chunk0, d_seq_nchunks,
+                                                                               d_seq_slot, d_state);
+        mingru_chunk_apply_kernel<T><<<dim3(gx, (unsigned)num_chunks), 128, 0, st>>>(
+            static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_chunk_start, d_chunk_len, AB,
+            static_cast<T*>(d_y));
+    });
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_gelu_inplace(void* d_x, int64_t n, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && n >= 0);
+    if (n == 0) return PA_OK;
+    PA_DISPATCH_ELEM(elem, gelu_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(static_cast<T*>(d_x), n));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_silu_mul(const void* d_gate_up, int64_t rows, int ff, void* d_out, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_gate_up && d_out && rows >= 0 && ff > 0);
+    if (rows == 0) return PA_OK;
+    const int64_t n = rows * ff;
+    PA_DISPATCH_ELEM(elem, silu_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               static_cast<const T*>(d_gate_up), rows, ff, static_cast<T*>(d_out)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_residual_combine(float* d_x, int64_t rows, int width, float mult, const void* d_mix, const void* d_dense,
+                               const float* d_routed, int top, const void* d_shared, const float* d_shared_gate,
+                               int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && rows >= 0 && width > 0 && (!d_routed || top > 0));
+    if (rows == 0) return PA_OK;
+    const int64_t n = rows * width;
+    PA_DISPATCH_ELEM(elem, residual_combine_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               d_x, rows, width, mult, static_cast<const T*>(d_mix), static_cast<const T*>(d_dense),
+                               d_routed, top, static_cast<const T*>(d_shared), d_shared_gate));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_gather_rows_f32(const float* d_src, const int32_t* d_rows, int n, int width, float* d_dst,
+                              pa_stream_t stream) {
+    PA_CHECK_ARG(d_src && d_rows && d_dst && n >= 0 && width > 0);
+    if (n == 0) return PA_OK;
+    gather_rows_kernel<float><<<n, 256, 0, as_stream(stream)>>>(d_src, d_rows, n, width, d_dst);
+    PA_RETURN_LAUNCH_STATUS();
+}

@@ -15,3 +15,9 @@ from .page_table import PageTable  # noqa: F401
 from . import sampling  # noqa: F401
 
 from .decoders import CUDADecoder, INT8Decoder  # noqa: F401
+
+# config-driven models: registry, ragged-batch engine, state manager
+from .registry import MODEL_REGISTRY, load_model, register_model  # noqa: F401,E402
+from .hybrid import HybridDecoder  # noqa: F401,E402
+from .engine import Engine, Scheduler, generate  # noqa: F401,E402
+from .seq_state import SequenceStateCache  # noqa: F401,E402

@@ -9,6 +9,7 @@ import os
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG, "libpa_b200.so")
+CORE_LIB_PATH = os.path.join(_PKG, "libpa_b200_core.so")   # build.py --core: the subset the config-driven models need
 
 PA_OK = 0
 PA_ERR_UNSUPPORTED = -2
@@ -99,6 +100,30 @@ _SIGS = {
     "pa_nccl_destroy": ([_vp], _i32),
     "pa_nccl_gather_bytes": ([_i32, _i32, _i32], _sz),
     "pa_nccl_allgather_combine": ([_vp, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _sz, _vp, _vp, _vp], _i32),
+    # ragged-batch sequence ops (seq_ops.cu, diff_attention.cu, moe_ops.cu)
+    "pa_linear_f32_exact": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp], _i32),
+    "pa_embedding_rows": ([_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp], _i32),
+    "pa_rms_norm_shift": ([_vp, _i32, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp], _i32),
+    "pa_rms_norm_state_store": ([_vp, _i32, _f32, _f32, _vp, _vp, _vp, _vp, _i32, _vp, _vp], _i32),
+    "pa_mingru_scan": ([_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _vp], _i32),
+    "pa_mingru_chunked_workspace_bytes": ([_i32, _i32], _sz),
+    "pa_mingru_scan_chunked": ([_vp, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _vp, _sz, _vp], _i32),
+    "pa_gelu_inplace": ([_vp, _i64, _i32, _vp], _i32),
+    "pa_silu_mul": ([_vp, _i64, _i32, _vp, _i32, _vp], _i32),
+    "pa_residual_combine": ([_vp, _i64, _i32, _f32, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _vp], _i32),
+    "pa_gather_rows_f32": ([_vp, _vp, _i32, _i32, _vp, _vp], _i32),
+    "pa_kv_append_rows": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _vp], _i32),
+    "pa_diff_attention_tile_tokens": ([_i32, _i32], _i32),
+    "pa_diff_attention_workspace_bytes": ([_i32, _i32, _i32, _i32, _i32], _sz),
+    "pa_diff_attention": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
+                           _f32, _f32, _i32, _f32, _f32, _f32, _vp, _i32, _i32, _vp, _sz, _vp], _i32),
+    "pa_router_topk": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp], _i32),
+    "pa_moe_tile_rows": ([], _i32),
+    "pa_moe_max_tiles": ([_i32, _i32], _i32),
+    "pa_moe_meta_ints": ([_i32, _i32], _sz),
+    "pa_moe_sort": ([_vp, _i32, _i32, _vp, _vp, _vp], _i32),
+    "pa_moe_gate_up": ([_vp, _i64, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp], _i32),
+    "pa_moe_down": ([_vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp], _i32),
 }
 
 EXPORTS = tuple(_SIGS)
@@ -109,16 +134,32 @@ class PAError(RuntimeError):
     pybind11 -> RuntimeError path, SURVEY 8b 'Errors')."""
 
 
+def _missing(name, path):
+    def fn(*_a, **_k):
+        raise PAError(f"{name} is not in {os.path.basename(path)} (the core build); build the full library with "
+                      f"`python build.py` in {_PKG}")
+    return fn
+
+
 def lib():
+    """The loaded library: libpa_b200.so, or, where only the core subset was built (build.py --core), that one --
+    entry points it does not hold raise PAError when called."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = LIB_PATH if os.path.exists(LIB_PATH) else CORE_LIB_PATH
+        if not os.path.exists(path):
             raise PAError(
                 f"{LIB_PATH} is missing: build it with `python build.py` in {_PKG} "
                 "(there is no CPU or PyTorch fallback for this path)")
-        handle = C.CDLL(LIB_PATH)
+        handle = C.CDLL(path)
         for name, (args, res) in _SIGS.items():
-            fn = getattr(handle, name)  # AttributeError if the header and the .so disagree
+            try:
+                fn = getattr(handle, name)
+            except AttributeError:
+                if path == LIB_PATH:
+                    raise  # the header and the full .so disagree
+                setattr(handle, name, _missing(name, path))
+                continue
             fn.argtypes = args
             fn.restype = res
         _lib = handle

@@ -1,0 +1,327 @@
+"""HybridDecoder -- a config-driven decoder stack over a ragged batch: every layer is one MIXER (picked by the layer's
+`type` from MIXERS) plus an optional FEED-FORWARD (picked by `mlp.kind` from FEED_FORWARDS) that both read the same
+pre-norm output; the residual stream is float.  The `Megusun` design is served by this class:
+
+    x      = embed[token]                                         (float residual)
+    h      = x / sqrt(mean(x^2) + eps) * g_l                      (one number g_l per layer)
+    hs     = h + (h_prev - h) * shift_l                           (token shift; h_prev carried per sequence)
+    x     += m * (mixer_l(hs) + ff_l(h))                          (m = residual_mult)
+    logits = head . (x / sqrt(mean(x^2) + eps) * g_final)
+
+  mixer 'mingru'     z = sigmoid(W_z hs + b_z), u = W_x hs + b_x, c = u + 1/2 (u >= 0) | sigmoid(u),
+                     S_t = (1 - z) S_{t-1} + z c,  out = W_o (S_t * silu(W_g hs))          state S per sequence, float
+  mixer 'attention'  differential attention over the paged K/V pools (csrc/diff_attention.cu), no rotation, a
+                     position-dependent query temperature, lambda = exp(lq1.lk1) - exp(lq2.lk2) + diff
+  ff 'dense'         W_down gelu_erf(W_up h)
+  ff 'moe'           sigmoid router, top-k by score, the score scales the expert's INPUT, experts W_down(silu(W_gate a) *
+                     W_up a), plus a shared expert gated by sigmoid(w_sg . h)
+
+Every size and constant comes from config.json (or a tensor's shape); the constants a design fixes are the arguments
+the mechanisms are constructed with.  Two precisions: 'bfloat16' (matrix products and their activations in bfloat16
+with float accumulation; norms, shift, recurrence, softmax, routers and the residual in float) and 'float32'
+(everything in IEEE float: the fp32 FMA linear kernels, no reduced-precision matrix mode).
+
+All compute is in libpa_b200.so kernels, except the plain bfloat16 matrix products, which go to the vendor GEMM
+(cuBLASLt through torch.nn.functional.linear).  Weight names: '<layer>.mix.*', '<layer>.mlp.*', '<layer>.norm1',
+'<layer>.shift', 'embed', 'final.norm', 'head' (linear weights [out, in])."""
+import json
+import math
+import os
+
+import torch
+
+from . import _cabi
+from .safetensors_io import load_file
+
+_ELEM = {torch.float32: 4, torch.bfloat16: 2}
+_KV = {torch.float32: "f32", torch.bfloat16: "bf16"}
+SCAN_CHUNK = 64           # tokens per chunk of the chunked recurrent scan
+SCAN_CHUNKED_FROM = 256   # portions at least this long use it
+
+
+def _chk(st, what):
+    _cabi.check(st, what)
+
+
+class _Ctx:
+    """What a layer needs from the model during one step."""
+
+    def __init__(self, model, batch):
+        self.model, self.batch, self.lib = model, batch, model._lib
+        self.dt, self.elem, self.dev = model.act_dtype, _ELEM[model.act_dtype], model.device
+        self.R = batch.rows
+
+    def empty(self, *shape, dtype=None):
+        return torch.empty(shape, dtype=dtype or self.dt, device=self.dev)
+
+
+# ---------------------------------------------------------------------------------------------------------------- mixers
+class MinGRUMixer:
+    """minGRU: gates read only the current token, so the three projections are one matrix product over the whole
+    batch and the recurrence is an elementwise scan (pa_mingru_scan / _chunked) over each portion from the state slot."""
+    kind = "mingru"
+
+    def __init__(self, model, prefix, cfg, W):
+        self.width = int(cfg["width"])
+        self.w_zxg = model._weight(torch.cat([W[prefix + "z"], W[prefix + "x"], W[prefix + "g"]], 0))
+        self.z_bias = model._f32(W[prefix + "z.b"])
+        self.x_bias = model._f32(W[prefix + "x.b"])
+        self.w_o = model._weight(W[prefix + "o"])
+        self.state = model.states.add_state(self.width)
+
+    def forward(self, c, hs):
+        b, lib, s = c.batch, c.lib, _cabi.stream()
+        zxg = c.model._linear(hs, self.w_zxg)
+        y = c.empty(c.R, self.width)
+        longest = max(p[1] for p in b.portions)
+        if longest >= SCAN_CHUNKED_FROM:
+            cs, cl, s0, sn, nch = b.scan_chunks(SCAN_CHUNK)
+            ws = c.empty(lib.pa_mingru_chunked_workspace_bytes(nch, self.width), dtype=torch.uint8)
+            _chk(lib.pa_mingru_scan_chunked(zxg.data_ptr(), self.z_bias.data_ptr(), self.x_bias.data_ptr(), self.width,
+                                            cs.data_ptr(), cl.data_ptr(), nch, s0.data_ptr(), sn.data_ptr(),
+                                            b.seq_slot.data_ptr(), b.num_seqs, self.state.data_ptr(), y.data_ptr(),
+                                            c.elem, ws.data_ptr(), ws.numel(), s), "pa_mingru_scan_chunked")
+        else:
+            _chk(lib.pa_mingru_scan(zxg.data_ptr(), self.z_bias.data_ptr(), self.x_bias.data_ptr(), self.width,
+                                    b.seq_start.data_ptr(), b.seq_len.data_ptr(), b.seq_slot.data_ptr(), b.num_seqs,
+                                    self.state.data_ptr(), y.data_ptr(), c.elem, s), "pa_mingru_scan")
+        return c.model._linear(y, self.w_o)
+
+
+class DiffAttentionMixer:
+    """Differential attention with grouped key/value heads over a paged pool of its own (KVTileCache with key rows
+    of 2 * dim and value rows of vdim)."""
+    kind = "attention"
+
+    def __init__(self, model, prefix, cfg, W):
+        self.heads, self.kv_heads = int(cfg["heads"]), int(cfg["kv_heads"])
+        self.dim, self.vdim = int(cfg["dim"]), int(cfg["vdim"])
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.scale = float(cfg["scale"])
+        self.diff = float(cfg["diff"])
+        qt = cfg.get("q_temp") or {}
+        self.temp_coef, self.temp_every = float(qt.get("coef", 0.0)), int(qt.get("every", 1))
+        f = lambda n: W[prefix + n].to(torch.float32)  # noqa: E731
+        self.lam = float(torch.exp((f("lq1") * f("lk1")).sum()) - torch.exp((f("lq2") * f("lk2")).sum())) + self.diff
+        self.w_qkv = model._weight(torch.cat([W[prefix + "q"], W[prefix + "k"], W[prefix + "v"]], 0))
+        self.w_o = model._weight(W[prefix + "o"])
+        self.q_cols = self.heads * 2 * self.dim
+        self.k_cols = self.kv_heads * 2 * self.dim
+        self.kv = model.states.add_kv_layer(self.kv_heads, 2 * self.dim, self.vdim, _KV[model.act_dtype])
+        self.tile_tokens = model._lib.pa_diff_attention_tile_tokens(self.heads, self.kv_heads)
+
+    def forward(self, c, hs):
+        b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
+        qkv = c.model._linear(hs, self.w_qkv)
+        kv.append_rows(qkv, self.q_cols, self.q_cols + self.k_cols, b.row_slot, b.row_pos)
+        tiles, ntiles, longest = b.query_tiles(self.tile_tokens)
+        out = c.empty(c.R, self.heads * self.vdim)
+        # few CTAs over a long context: cut the keys so the chip is filled (32 keys per step, >= 8 steps per part)
+        ctas = ntiles * self.kv_heads * max(1, math.ceil(self.heads // self.kv_heads / 32))
+        nsplit = 1
+        if ctas < 2 * c.model.sm_count and longest > 512:
+            nsplit = max(1, min(2 * c.model.sm_count // ctas, longest // 256, 64))
+        ws = None
+        if nsplit > 1:
+            ws = c.empty(lib.pa_diff_attention_workspace_bytes(ntiles, self.heads, self.kv_heads, self.vdim, nsplit),
+                         dtype=torch.uint8)
+        pt = kv.page_table_
+        _chk(lib.pa_diff_attention(qkv.data_ptr(), qkv.stride(0), 0, kv.key_buffer_.data_ptr(), kv.value_buffer_.data_ptr(),
+                                   pt.device_data().data_ptr(), pt.num_beams_, pt.num_heads_, pt.num_tiles_,
+                                   kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, self.heads, self.dim,
+                                   self.vdim, self.scale, self.temp_coef, self.temp_every, self.lam, 1.0 - self.diff,
+                                   c.model.eps, out.data_ptr(), c.elem, nsplit, _cabi.ptr(ws),
+                                   ws.numel() if ws is not None else 0, s), "pa_diff_attention")
+        return c.model._linear(out, self.w_o)
+
+
+MIXERS = {"mingru": MinGRUMixer, "attention": DiffAttentionMixer}
+
+
+# --------------------------------------------------------------------------------------------------------- feed-forwards
+class DenseFF:
+    kind = "dense"
+
+    def __init__(self, model, prefix, cfg, W):
+        self.w_up = model._weight(W[prefix + "up"])
+        self.w_down = model._weight(W[prefix + "down"])
+
+    def forward(self, c, h):
+        a = c.model._linear(h, self.w_up)
+        _chk(c.lib.pa_gelu_inplace(a.data_ptr(), a.numel(), c.elem, _cabi.stream()), "pa_gelu_inplace")
+        return dict(dense=c.model._linear(a, self.w_down))
+
+
+class MoEFF:
+    """Routed experts: scores = sigmoid(router logits), the `top` largest, not renormalised, applied to the expert's
+    input; grouped matrix products over the pairs sorted by expert (csrc/moe_ops.cu); optional gated shared expert."""
+    kind = "moe"
+
+    def __init__(self, model, prefix, cfg, W):
+        self.experts, self.top = int(cfg["router"]["experts"]), int(cfg["router"]["top"])
+        self.ff = int(cfg["expert"]["ff"])
+        ex = lambda n: [W[f"{prefix}e{e}.{n}"] for e in range(self.experts)]  # noqa: E731
+        self.w_gate_up = model._weight_raw(torch.stack([torch.cat([g, u], 0) for g, u in zip(ex("gate"), ex("up"))]))
+        self.w_down = model._weight_raw(torch.stack(ex("down")))
+        self.w_router = model._f32(W[prefix + "router"])
+        self.shared = None
+        if cfg.get("shared"):
+            sp = prefix + "shared."
+            self.shared = dict(w_gate_up=model._weight(torch.cat([W[sp + "gate"], W[sp + "up"]], 0)),
+                               w_down=model._weight(W[sp + "down"]), ff=int(cfg["shared"]["ff"]),
+                               w_sg=model._f32(W[sp + "sg"].reshape(-1)) if sp + "sg" in W else None)
+
+    def forward(self, c, h):
+        lib, R, s, wdt = c.lib, c.R, _cabi.stream(), c.model.width
+        i32, f32 = dict(dtype=torch.int32), dict(dtype=torch.float32)
+        pairs = R * self.top
+        sel_id, sel_w = c.empty(pairs, **i32), c.empty(pairs, **f32)
+        sh = self.shared
+        sgate = c.empty(R, **f32) if sh and sh["w_sg"] is not None else None
+        _chk(lib.pa_router_topk(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(sh["w_sg"]) if sgate is not None else None,
+                                R, wdt, self.experts, self.top, 0, 0, sel_id.data_ptr(), sel_w.data_ptr(),
+                                _cabi.ptr(sgate), c.elem, s), "pa_router_topk")
+        order = c.empty(pairs, **i32)
+        meta = c.empty(lib.pa_moe_meta_ints(pairs, self.experts), **i32)
+        _chk(lib.pa_moe_sort(sel_id.data_ptr(), pairs, self.experts, order.data_ptr(), meta.data_ptr(), s), "pa_moe_sort")
+        act = c.empty(pairs, self.ff)
+        _chk(lib.pa_moe_gate_up(h.data_ptr(), h.stride(0), self.w_gate_up.data_ptr(), wdt, self.ff, self.experts,
+                                order.data_ptr(), sel_w.data_ptr(), self.top, meta.data_ptr(), pairs, act.data_ptr(),
+                                c.elem, s), "pa_moe_gate_up")
+        routed = c.empty(pairs, wdt, **f32)
+        _chk(lib.pa_moe_down(act.data_ptr(), self.w_down.data_ptr(), self.ff, wdt, self.experts, order.data_ptr(),
+                             meta.data_ptr(), pairs, routed.data_ptr(), c.elem, s), "pa_moe_down")
+        out = dict(routed=routed, top=self.top)
+        if sh:
+            gu = c.model._linear(h, sh["w_gate_up"])
+            a = c.empty(R, sh["ff"])
+            _chk(lib.pa_silu_mul(gu.data_ptr(), R, sh["ff"], a.data_ptr(), c.elem, s), "pa_silu_mul")
+            out.update(shared=c.model._linear(a, sh["w_down"]), shared_gate=sgate)
+        return out
+
+
+FEED_FORWARDS = {"dense": DenseFF, "moe": MoEFF}
+
+
+class _Layer:
+    pass
+
+
+class HybridDecoder:
+    ARCHITECTURES = ("Megusun",)
+
+    def __init__(self, config, weights, dtype="bfloat16", *, max_tokens=4096, max_seqs=4, tile_size=16, device=None):
+        from .seq_state import SequenceStateCache
+        self.act_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[str(dtype).replace("torch.", "")]
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._lib = _cabi.lib()
+        self.sm_count = _cabi.device_info()[0]
+        self.config = config
+        self.width, self.vocab = int(config["width"]), int(config["vocab"])
+        self.eps = float(config["norm"]["eps"])
+        self.mult = float(config.get("residual_mult", 1.0))
+        self.states = SequenceStateCache(max_seqs, max_tokens, tile_size, self.device)
+        self._ws = None
+        W = weights
+        if tuple(W["embed"].shape) != (self.vocab, self.width):
+            raise ValueError("embed does not match config vocab / width")
+        self.embed = W["embed"].to(self.device, self.act_dtype).contiguous()
+        self.head = self._weight(W["head"])
+        self.final_gain = float(W["final.norm"].to(torch.float32))
+        self.layers = []
+        for i, lc in enumerate(config["layers"]):
+            L = _Layer()
+            p = f"l{i}."
+            L.gain = float(W[p + "norm1"].to(torch.float32))
+            L.shift = self._f32(W[p + "shift"]) if p + "shift" in W else None
+            L.prev = self.states.add_state(self.width) if L.shift is not None else None
+            if lc["type"] not in MIXERS:
+                raise ValueError(f"unknown mixer type {lc['type']!r}")
+            L.mixer = MIXERS[lc["type"]](self, p + "mix.", lc.get("mixer") or {}, W)
+            mc = lc.get("mlp")
+            L.ff = None
+            if mc:
+                if mc["kind"] not in FEED_FORWARDS:
+                    raise ValueError(f"unknown feed-forward kind {mc['kind']!r}")
+                L.ff = FEED_FORWARDS[mc["kind"]](self, p + "mlp.", mc, W)
+            self.layers.append(L)
+
+    @classmethod
+    def from_pretrained(cls, path, dtype="bfloat16", **kw):
+        with open(os.path.join(path, "config.json")) as f:
+            config = json.load(f)
+        return cls(config, load_file(os.path.join(path, "model.safetensors")), dtype, **kw)
+
+    # ---- weights ----------------------------------------------------------------------------------------------------
+    def _f32(self, t):
+        return t.to(torch.float32).to(self.device).contiguous()
+
+    def _weight_raw(self, t):
+        """[.., out, in] in the activation type (the grouped kernels read the stored orientation)."""
+        return t.to(self.act_dtype).to(self.device).contiguous()
+
+    def _weight(self, t):
+        """A linear layer's weight for _linear: bfloat16 keeps [out, in] (vendor GEMM, transposed operand); float32
+        is stored [in, out], the layout of the fp32 linear kernels."""
+        if self.act_dtype == torch.float32:
+            return t.to(torch.float32).t().contiguous().to(self.device)
+        return self._weight_raw(t)
+
+    def _linear(self, x, w, out_dtype=None):
+        R = x.shape[0]
+        if self.act_dtype == torch.float32:
+            K, N = w.shape
+            out = torch.empty((R, N), dtype=torch.float32, device=self.device)
+            need = self._lib.pa_linear_workspace_bytes(R, K, N)
+            if need and (self._ws is None or self._ws.numel() < need):
+                self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            _chk(self._lib.pa_linear_f32_exact(x.data_ptr(), w.data_ptr(), None, R, K, N, 0, out.data_ptr(),
+                                               _cabi.ptr(self._ws) if need else None, self._ws.numel() if need else 0,
+                                               _cabi.stream()), "pa_linear_f32_exact")
+            return out
+        if out_dtype == torch.float32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.nn.functional.linear(x, w)
+
+    # ---- the step ---------------------------------------------------------------------------------------------------
+    def forward(self, batch, want_rows=None):
+        """Run the rows of `batch` through the stack from the cache / state earlier steps left (and leave theirs).
+        want_rows: int32 device tensor of rows whose logits are wanted (None: all).  Returns float logits
+        [len(want_rows), vocab]."""
+        c = _Ctx(self, batch)
+        lib, R, W, s = self._lib, batch.rows, self.width, _cabi.stream()
+        x = torch.empty((R, W), dtype=torch.float32, device=self.device)
+        _chk(lib.pa_embedding_rows(self.embed.data_ptr(), c.elem, batch.ids.data_ptr(), R, W, self.vocab, x.data_ptr(), s),
+             "pa_embedding_rows")
+        for L in self.layers:
+            h = c.empty(R, W)
+            hs = c.empty(R, W) if L.shift is not None else None
+            _chk(lib.pa_rms_norm_shift(x.data_ptr(), R, W, self.eps, L.gain, None, _cabi.ptr(L.shift),
+                                       batch.row_prev.data_ptr(), batch.row_slot.data_ptr(), _cabi.ptr(L.prev),
+                                       h.data_ptr(), _cabi.ptr(hs), c.elem, s), "pa_rms_norm_shift")
+            if L.shift is not None:
+                _chk(lib.pa_rms_norm_state_store(x.data_ptr(), W, self.eps, L.gain, None, batch.seq_start.data_ptr(),
+                                                 batch.seq_len.data_ptr(), batch.seq_slot.data_ptr(), batch.num_seqs,
+                                                 L.prev.data_ptr(), s), "pa_rms_norm_state_store")
+            mix = L.mixer.forward(c, hs if hs is not None else h)
+            ff = L.ff.forward(c, h) if L.ff is not None else {}
+            _chk(lib.pa_residual_combine(x.data_ptr(), R, W, self.mult, mix.data_ptr(), _cabi.ptr(ff.get("dense")),
+                                         _cabi.ptr(ff.get("routed")), ff.get("top", 1), _cabi.ptr(ff.get("shared")),
+                                         _cabi.ptr(ff.get("shared_gate")), c.elem, s), "pa_residual_combine")
+            if self.layer_hook is not None:
+                self.layer_hook(x)
+        if want_rows is not None:
+            n = want_rows.numel()
+            xs = torch.empty((n, W), dtype=torch.float32, device=self.device)
+            _chk(lib.pa_gather_rows_f32(x.data_ptr(), want_rows.data_ptr(), n, W, xs.data_ptr(), s), "pa_gather_rows_f32")
+        else:
+            n, xs = R, x
+        if n == 0:
+            return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
+        hf = torch.empty((n, W), dtype=self.act_dtype, device=self.device)
+        _chk(lib.pa_rms_norm_shift(xs.data_ptr(), n, W, self.eps, self.final_gain, None, None, None, None, None,
+                                   hf.data_ptr(), None, c.elem, s), "pa_rms_norm_shift")
+        return self._linear(hf, self.head, out_dtype=torch.float32)
+
+    layer_hook = None   # debugging aid: called with the float residual after every layer

@@ -4,8 +4,12 @@ Mirrors kv_cache/kv_tile_cache.hpp:9-80 / kv_tile_cache.cpp:7-128: two device po
 (`key_buffer_`, `value_buffer_`) of `total_pages * tile_size * head_dim` elements, page p
 of either pool starting at element p*tile_size*head_dim (cpp:52-62), K and V of a tile
 sharing one page id.  Storage dtype: 'f16' (fp16 pages, KVTileCache<half>), 'f32' (fp32 pages,
-KVTileCache<float> -- the two instantiations of kv_tile_cache.cpp:127-128) or 'i8' (int8 pages plus
-one f32 scale per (page, row) for K and for V).
+KVTileCache<float> -- the two instantiations of kv_tile_cache.cpp:127-128), 'i8' (int8 pages plus
+one f32 scale per (page, row) for K and for V) or 'bf16' (bfloat16 pages, written and read by the ragged-batch
+kernels only).  `init(..., value_dim=)` gives the V pool its own row width (attention whose key rows hold more
+than one map, or whose values are wider than its keys); the per-request lifecycle of a serving engine is
+`register_tile` as tokens arrive and `release_beam` when the request ends, with `evict_on_exhaustion = False`
+so that a full pool is an error instead of the silent loss of a live request's oldest tile.
 
 Decisions taken where the reference contradicts itself: page ids come
 from a free list (the reference's `map.size()` re-issues live ids after an eviction),
@@ -23,18 +27,19 @@ import torch
 from . import _cabi
 from .page_table import PageTable
 
-_DTYPES = {"f16": torch.float16, "i8": torch.int8, "f32": torch.float32}
+_DTYPES = {"f16": torch.float16, "i8": torch.int8, "f32": torch.float32, "bf16": torch.bfloat16}
 
 
 class KVTileCache:
     def __init__(self, dtype="f16", device=None):
         if dtype not in _DTYPES:
-            raise ValueError("KVTileCache dtype must be 'f16', 'i8' or 'f32'")
+            raise ValueError("KVTileCache dtype must be 'f16', 'i8', 'f32' or 'bf16'")
         self.dtype = dtype
         self._device = torch.device(device) if device is not None else None
         self.key_buffer_ = self.value_buffer_ = None
         self.k_scales_ = self.v_scales_ = None
-        self.tile_size_ = self.head_dim_ = self.total_pages_ = 0
+        self.tile_size_ = self.head_dim_ = self.value_dim_ = self.total_pages_ = 0
+        self.evict_on_exhaustion = True   # the reference's LRU rule; False: a full pool raises
         self.page_table_ = PageTable(device)
         self.tile_to_page_map_ = OrderedDict()  # (beam, head, tile) -> page, LRU order (oldest first)
         self._free = []
@@ -43,10 +48,12 @@ class KVTileCache:
         self._ws = {}         # decode scratch, one buffer per stream (the chunk counter and partials live in it)
 
     # ---- kv_tile_cache.cpp:18-24, 39-50 ------------------------------------------------
-    def init(self, num_pages, tile_size, head_dim):
-        if min(num_pages, tile_size, head_dim) <= 0:
+    def init(self, num_pages, tile_size, head_dim, value_dim=None):
+        value_dim = head_dim if value_dim is None else value_dim
+        if min(num_pages, tile_size, head_dim, value_dim) <= 0:
             raise ValueError("KVTileCache.init: sizes must be positive")
         self.tile_size_, self.head_dim_, self.total_pages_ = int(tile_size), int(head_dim), int(num_pages)
+        self.value_dim_ = int(value_dim)
         self._allocate_buffers()
         self._reset_allocator()
         self.page_table_.clear()  # a table configured before a re-init must not keep ids of the old pool
@@ -68,7 +75,8 @@ class KVTileCache:
         shape = (self.total_pages_, self.tile_size_, self.head_dim_)
         dev = self._dev()
         self.key_buffer_ = torch.zeros(shape, dtype=_DTYPES[self.dtype], device=dev)
-        self.value_buffer_ = torch.zeros(shape, dtype=_DTYPES[self.dtype], device=dev)
+        self.value_buffer_ = torch.zeros(shape[:2] + (self.value_dim_ or self.head_dim_,), dtype=_DTYPES[self.dtype],
+                                         device=dev)
         if self.dtype == "i8":
             self.k_scales_ = torch.ones(shape[:2], dtype=torch.float32, device=dev)
             self.v_scales_ = torch.ones(shape[:2], dtype=torch.float32, device=dev)
@@ -78,6 +86,7 @@ class KVTileCache:
         assert key_buffer.shape == value_buffer.shape and key_buffer.is_contiguous() and value_buffer.is_contiguous()
         assert key_buffer.dtype == _DTYPES[self.dtype]
         self.total_pages_, self.tile_size_, self.head_dim_ = key_buffer.shape
+        self.value_dim_ = self.head_dim_
         self.key_buffer_, self.value_buffer_ = key_buffer, value_buffer
         self.k_scales_, self.v_scales_ = k_scales, v_scales
         self._reset_allocator()
@@ -99,7 +108,8 @@ class KVTileCache:
         return self.key_buffer_.data_ptr() + self._page_offset_bytes(page_id)
 
     def get_value_ptr(self, page_id):
-        return self.value_buffer_.data_ptr() + self._page_offset_bytes(page_id)
+        assert 0 <= page_id < self.total_pages_, "page_id out of range"
+        return self.value_buffer_.data_ptr() + page_id * self.tile_size_ * self.value_dim_ * self.value_buffer_.element_size()
 
     # ---- kv_tile_cache.cpp:65-98 -------------------------------------------------------
     def register_tile(self, beam_id, head_id, tile_id):
@@ -117,10 +127,42 @@ class KVTileCache:
             return page
 
     def _evict_if_needed(self):
-        while not self._free and self.tile_to_page_map_:
+        while self.evict_on_exhaustion and not self._free and self.tile_to_page_map_:
             last, page = self.tile_to_page_map_.popitem(last=False)  # least recently used
             self.page_table_.remove(*last)
             self._release_page(page)  # a page still shared by another beam is not freed yet
+
+    def release_beam(self, beam_id):
+        """Give back every tile of table row `beam_id` (a request that ended): entries cleared on the host mirror and,
+        at the next flush, on the device; pages return to the free list (a page still shared with another row only
+        loses this reference).  Returns the number of tiles released."""
+        beam_id = int(beam_id)
+        with self.mutex_:
+            keys = [k for k in self.tile_to_page_map_ if k[0] == beam_id]
+            for k in keys:
+                page = self.tile_to_page_map_.pop(k)
+                self.page_table_.remove(*k)
+                self._release_page(page)
+        return len(keys)
+
+    def free_pages(self):
+        return len(self._free)
+
+    def append_rows(self, src, k_off, v_off, row_slot, row_pos):
+        """K/V rows straight out of a projection buffer `src` [R, stride] (pool dtype): the key of kv head g at columns
+        k_off + g * head_dim, its value at v_off + g * value_dim; row r goes to position row_pos[r] of table row
+        row_slot[r] (int32 device tensors).  Pools 'f32' and 'bf16'."""
+        if self.dtype not in ("f32", "bf16"):
+            raise ValueError("append_rows serves 'f32' and 'bf16' pools")
+        assert src.dtype == self.key_buffer_.dtype and src.dim() == 2 and src.stride(1) == 1
+        pt = self.page_table_
+        table = pt.device_data()
+        with torch.cuda.device(table.device):
+            _cabi.check(_cabi.lib().pa_kv_append_rows(
+                self.key_buffer_.data_ptr(), self.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_,
+                pt.num_heads_, pt.num_tiles_, self.total_pages_, self.tile_size_, self.head_dim_, self.value_dim_,
+                src.data_ptr(), src.stride(0), int(k_off), int(v_off), row_slot.data_ptr(), row_pos.data_ptr(),
+                src.shape[0], src.element_size(), _cabi.stream()), "pa_kv_append_rows")
 
     def sync_page_table_to_gpu(self):
         self.page_table_.sync_to_gpu()
@@ -251,6 +293,7 @@ class KVTileCache:
                 new_v, rv = pipe.upload(new_v, "new_v")
             releases = [rk, rv]
         R = new_k.shape[0]
+        assert self.value_dim_ == self.head_dim_ and self.dtype != "bf16", "append(): equal K/V widths, f16/f32/i8 pools"
         assert new_k.is_contiguous() and new_v.is_contiguous() and new_k.shape == new_v.shape
         assert new_k.shape[1] == pt.num_heads_ and new_k.shape[2] == self.head_dim_
         lib = _cabi.lib()
