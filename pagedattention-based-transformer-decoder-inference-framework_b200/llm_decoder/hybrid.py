@@ -311,14 +311,14 @@ class HybridDecoder:
                                          _cabi.ptr(ff.get("shared_gate")), c.elem, s), "pa_residual_combine")
             if self.layer_hook is not None:
                 self.layer_hook(x)
+        if want_rows is not None and want_rows.numel() == 0:
+            return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
         if want_rows is not None:
             n = want_rows.numel()
             xs = torch.empty((n, W), dtype=torch.float32, device=self.device)
             _chk(lib.pa_gather_rows_f32(x.data_ptr(), want_rows.data_ptr(), n, W, xs.data_ptr(), s), "pa_gather_rows_f32")
         else:
             n, xs = R, x
-        if n == 0:
-            return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
         hf = torch.empty((n, W), dtype=self.act_dtype, device=self.device)
         _chk(lib.pa_rms_norm_shift(xs.data_ptr(), n, W, self.eps, self.final_gain, None, None, None, None, None,
                                    hf.data_ptr(), None, c.elem, s), "pa_rms_norm_shift")
