@@ -23,6 +23,8 @@ extra  = the other BASELINE.json configurations under the same clock (benchmarks
          sample: c4_int8_decode, c4_gemm_pair (+ an int8 library peak measured in the same run), c3_group, c2_fp32_mlp,
          c5_splitkv (one 128K-token sequence split over the N ranks: decode + merge + exchange in ONE launch, the
          stand-alone peer-memory exchange, and the NCCL all-gather form).  --no-extra skips them.
+--hybrid: a different workload altogether (benchmarks/hybrid.py): the config-driven hybrid stack against CUDADecoder at
+         equal size; the default workload and its JSON contract are untouched by it.
 N > 1: one process per GPU (torchrun), rows sharded across ranks, no data-path collective in the headline
          step; c5_splitkv is the mode with an exchange.
 """
@@ -59,6 +61,10 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default="overlap", choices=["overlap", "fused"])
     ap.add_argument("--no-extra", action="store_true", help="skip the C3 / C4 / C5 extra block")
+    ap.add_argument("--hybrid", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the config-driven hybrid stack "
+                         "(design Megusun) at realistic layer sizes next to CUDADecoder at equal size, and its kernels "
+                         "against their rooflines (benchmarks/hybrid.py); one JSON line")
     return ap.parse_args()
 
 
@@ -433,6 +439,10 @@ def run_ours(args):
 
 def main():
     args = parse()
+    if args.hybrid:
+        from benchmarks import hybrid
+        print(json.dumps({"bench": "hybrid", **hybrid.run()}, default=float))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -70,9 +70,12 @@ __global__ void kv_append_rows_kernel(T* __restrict__ k_pool, T* __restrict__ v_
     for (int d = lane; d < v_dim; d += 32) v_pool[prow * v_dim + d] = sv[d];
 }
 
-// Difference of the two maps, head-wise RMS norm and the output factor for one row held across a warp
-// (value column lane + 32 i in slot i).
-template <typename T, int NV>
+// Difference of the two maps, head-wise RMS norm and the output factor for one row held across a warp: slot i of a lane
+// is value column lane + 32 i (PACKED false) or lane * NV + i (PACKED true).
+template <int NV, bool PACKED>
+__device__ __forceinline__ int da_col(int lane, int i) { return PACKED ? lane * NV + i : lane + 32 * i; }
+
+template <typename T, int NV, bool PACKED = false>
 __device__ __forceinline__ void da_finish_row(const float (&a1)[NV], const float (&a2)[NV], float l1, float l2,
                                               const DiffAttnParams& p, int lane, T* __restrict__ dst) {
     float o[NV];
@@ -80,7 +83,7 @@ __device__ __forceinline__ void da_finish_row(const float (&a1)[NV], const float
     const float i1 = 1.0f / l1, i2 = 1.0f / l2;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const bool ok = lane + 32 * i < p.vdim;
+        const bool ok = da_col<NV, PACKED>(lane, i) < p.vdim;
         o[i] = ok ? a1[i] * i1 - p.lambda * (a2[i] * i2) : 0.f;
         ss = fmaf(o[i], o[i], ss);
     }
@@ -88,7 +91,7 @@ __device__ __forceinline__ void da_finish_row(const float (&a1)[NV], const float
     const float rn = 1.0f / sqrtf(ss / (float)p.vdim + p.eps);
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-        if (lane + 32 * i < p.vdim) dst[lane + 32 * i] = from_f32<T>(o[i] * rn * p.out_mult);
+        if (da_col<NV, PACKED>(lane, i) < p.vdim) dst[da_col<NV, PACKED>(lane, i)] = from_f32<T>(o[i] * rn * p.out_mult);
 }
 
 template <typename T, int NV>
@@ -285,6 +288,265 @@ __global__ void __launch_bounds__(kDaWarps * 32) diff_attention_merge_kernel(con
     }
 }
 
+
+// ---- single-token tiles (decode) ------------------------------------------------------------------------------------
+// One CTA = one token x one key/value head x one part of the context; its R >= heads-per-kv-head rows are the query
+// heads of the group.  Nothing is staged: each of the 8 warps takes every 8th run of 32 keys, a lane reads ITS key's row
+// with 16-byte loads straight into the two dot products of every row (queries broadcast from shared memory), the warp
+// does the online softmax, then lanes switch to value columns and read each key's value row coalesced.  The 8 warps'
+// (m, l, acc) are merged through shared memory; nsplit > 1 leaves the CTA's partial for diff_attention_merge_kernel.
+// Needs dim a multiple of the 16-byte vector and R * NV <= 32 (the dispatcher falls back to the tile kernel otherwise).
+template <typename T> struct DaVec { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void da_load16(const T* __restrict__ p, float (&f)[DaVec<T>::N]) {
+    const uint4 v = ldg_stream_128(p);
+    if (sizeof(T) == 4) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+
+// NV consecutive values of a row starting at element lane * NV (NV * sizeof(T) is 4, 8, 16 or 32 bytes)
+template <typename T, int NV>
+__device__ __forceinline__ void da_load_packed(const T* __restrict__ p, float (&f)[NV]) {
+    constexpr int BYTES = NV * sizeof(T);
+    if (BYTES >= 16) {
+#pragma unroll
+        for (int c = 0; c < BYTES / 16; ++c) {
+            float t[DaVec<T>::N];
+            da_load16<T>(p + c * DaVec<T>::N, t);
+#pragma unroll
+            for (int i = 0; i < DaVec<T>::N; ++i) f[c * DaVec<T>::N + i] = t[i];
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) f[i] = to_f32<T>(p[i]);
+    }
+}
+
+template <typename T, int R, int NV, bool PACKED>
+__global__ void __launch_bounds__(kDaWarps * 32) diff_attention_decode_kernel(const DiffAttnParams p) {
+    extern __shared__ float smem[];
+    constexpr int VN = DaVec<T>::N;
+    const int kd = 2 * p.dim;
+    float* Qs = smem;                                   // [R][kd]
+    float* Ps = Qs + R * kd;                            // [warps][R][4 + 2 * vdim]
+    const int pstride = 4 + 2 * p.vdim;
+    const int hpg = p.heads / p.num_kv_heads;
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], slot = tile[2], pos = tile[3];
+    const int g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* kp = static_cast<const T*>(p.k_pool);
+    const T* vp = static_cast<const T*>(p.v_pool);
+    {
+        const float temp = 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f);
+        for (int idx = threadIdx.x; idx < R * kd; idx += blockDim.x) {
+            const int r = idx / kd, d = idx % kd;
+            float v = 0.f;
+            if (r < hpg)
+                v = to_f32<T>(static_cast<const T*>(p.q)[(int64_t)row0 * p.q_stride + p.q_off + (int64_t)(g * hpg + r) * kd + d]) * temp;
+            Qs[idx] = v;
+        }
+    }
+    __syncthreads();
+    float m1[R], l1[R], m2[R], l2[R], a1[R][NV], a2[R][NV];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        m1[r] = m2[r] = -INFINITY;
+        l1[r] = l2[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) a1[r][i] = a2[r][i] = 0.f;
+    }
+    const int total = pos + 1;
+    const int nsteps = (total + kDaKeys - 1) / kDaKeys;
+    const int per = (nsteps + p.nsplit - 1) / p.nsplit;
+    const int s_begin = blockIdx.z * per, s_end = min(nsteps, s_begin + per);
+    const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
+    for (int st = s_begin + warp; st < s_end; st += kDaWarps) {
+        const int j = st * kDaKeys + lane;
+        int prow = -1;                                  // pool row of this lane's key
+        if (j < total && j / p.tile_size < p.num_tiles) {
+            const int page = trow[j / p.tile_size];
+            if (page >= 0 && page < p.total_pages) prow = page * p.tile_size + j % p.tile_size;
+        }
+        float s1[R], s2[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) s1[r] = s2[r] = 0.f;
+        if (prow >= 0) {
+            const T* kr = kp + (int64_t)prow * kd;
+#pragma unroll 2
+            for (int d0 = 0; d0 < p.dim; d0 += VN) {
+                float k1[VN], k2[VN];
+                da_load16<T>(kr + d0, k1);
+                da_load16<T>(kr + p.dim + d0, k2);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float* q1 = Qs + r * kd + d0;
+                    const float* q2 = q1 + p.dim;
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) {
+                        s1[r] = fmaf(q1[i], k1[i], s1[r]);
+                        s2[r] = fmaf(q2[i], k2[i], s2[r]);
+                    }
+                }
+            }
+        }
+        const bool vis = prow >= 0;
+        float p1[R], p2[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float v1 = vis ? s1[r] * p.scale : -INFINITY, v2 = vis ? s2[r] * p.scale : -INFINITY;
+            const float n1 = fmaxf(m1[r], warp_max(v1)), n2 = fmaxf(m2[r], warp_max(v2));
+            const float c1 = n1 == -INFINITY ? 1.f : expf(m1[r] - n1), c2 = n2 == -INFINITY ? 1.f : expf(m2[r] - n2);
+            p1[r] = vis ? expf(v1 - n1) : 0.f;
+            p2[r] = vis ? expf(v2 - n2) : 0.f;
+            l1[r] = l1[r] * c1 + warp_sum(p1[r]);
+            l2[r] = l2[r] * c2 + warp_sum(p2[r]);
+            m1[r] = n1;
+            m2[r] = n2;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                a1[r][i] *= c1;
+                a2[r][i] *= c2;
+            }
+        }
+        const int nk = min(kDaKeys, total - st * kDaKeys);
+#pragma unroll 4
+        for (int jj = 0; jj < nk; ++jj) {
+            const int pr = __shfl_sync(0xffffffffu, prow, jj);
+            float v[NV];
+            if (pr >= 0) {
+                const T* vr = vp + (int64_t)pr * p.vdim;
+                if (PACKED) {
+                    da_load_packed<T, NV>(vr + lane * NV, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < p.vdim ? to_f32<T>(vr[lane + 32 * i]) : 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float w1 = __shfl_sync(0xffffffffu, p1[r], jj), w2 = __shfl_sync(0xffffffffu, p2[r], jj);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    a1[r][i] = fmaf(w1, v[i], a1[r][i]);
+                    a2[r][i] = fmaf(w2, v[i], a2[r][i]);
+                }
+            }
+        }
+    }
+    // ---- the warps' partials -> shared memory, merged by warp r for row r
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float* dst = Ps + ((int64_t)warp * R + r) * pstride;
+        if (lane == 0) {
+            dst[0] = m1[r]; dst[1] = l1[r]; dst[2] = m2[r]; dst[3] = l2[r];
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = da_col<NV, PACKED>(lane, i);
+            if (c < p.vdim) {
+                dst[4 + c] = a1[r][i];
+                dst[4 + p.vdim + c] = a2[r][i];
+            }
+        }
+    }
+    __syncthreads();
+    for (int r = warp; r < R; r += kDaWarps) {
+        if (r >= hpg) continue;
+        float M1 = -INFINITY, M2 = -INFINITY;
+        for (int w = 0; w < kDaWarps; ++w) {
+            M1 = fmaxf(M1, Ps[((int64_t)w * R + r) * pstride + 0]);
+            M2 = fmaxf(M2, Ps[((int64_t)w * R + r) * pstride + 2]);
+        }
+        float L1 = 0.f, L2 = 0.f, b1[NV], b2[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) b1[i] = b2[i] = 0.f;
+        for (int w = 0; w < kDaWarps; ++w) {
+            const float* pw = Ps + ((int64_t)w * R + r) * pstride;
+            const float w1 = pw[0] == -INFINITY ? 0.f : expf(pw[0] - M1), w2 = pw[2] == -INFINITY ? 0.f : expf(pw[2] - M2);
+            L1 = fmaf(w1, pw[1], L1);
+            L2 = fmaf(w2, pw[3], L2);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = da_col<NV, PACKED>(lane, i);
+                if (c < p.vdim) {
+                    b1[i] = fmaf(w1, pw[4 + c], b1[i]);
+                    b2[i] = fmaf(w2, pw[4 + p.vdim + c], b2[i]);
+                }
+            }
+        }
+        if (p.nsplit > 1) {
+            float* dst = p.partial + ((((int64_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit + blockIdx.z) * kDaRows + r) * pstride;
+            if (lane == 0) {
+                dst[0] = M1; dst[1] = L1; dst[2] = M2; dst[3] = L2;
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = da_col<NV, PACKED>(lane, i);
+                if (c < p.vdim) {
+                    dst[4 + c] = b1[i];
+                    dst[4 + p.vdim + c] = b2[i];
+                }
+            }
+        } else {
+            T* dst = static_cast<T*>(p.out) + (int64_t)row0 * p.heads * p.vdim + (int64_t)(g * hpg + r) * p.vdim;
+            da_finish_row<T, NV, PACKED>(b1, b2, L1, L2, p, lane, dst);
+        }
+    }
+}
+
+template <typename T, int R, int NV>
+static int da_decode_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    const size_t smem = ((size_t)R * 2 * p.dim + (size_t)kDaWarps * R * (4 + 2 * p.vdim)) * sizeof(float);
+    if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
+    const bool packed = p.vdim == 32 * NV && (NV * sizeof(T)) % 4 == 0 && (NV * sizeof(T) <= 16 || (NV * sizeof(T)) % 16 == 0);
+    auto kern = packed ? diff_attention_decode_kernel<T, R, NV, true> : diff_attention_decode_kernel<T, R, NV, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((unsigned)ntiles, (unsigned)p.num_kv_heads, (unsigned)p.nsplit);
+    kern<<<grid, kDaWarps * 32, smem, st>>>(p);
+    if (p.nsplit > 1) {
+        dim3 g2((unsigned)ntiles, (unsigned)p.num_kv_heads);
+        diff_attention_merge_kernel<T, NV><<<g2, kDaWarps * 32, 0, st>>>(p);
+    }
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+// PA_ERR_UNSUPPORTED: this shape stays on the tile kernel
+template <typename T>
+static int da_decode_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    const int hpg = p.heads / p.num_kv_heads, nv = (p.vdim + 31) / 32;
+    if (p.dim % DaVec<T>::N || hpg > 8 || nv > 8) return PA_ERR_UNSUPPORTED;
+    if ((uintptr_t)p.k_pool % 16 || (uintptr_t)p.v_pool % 16) return PA_ERR_UNSUPPORTED;
+    const int NVc = nv <= 1 ? 1 : nv <= 2 ? 2 : nv <= 4 ? 4 : 8;
+    if (hpg <= 4) {
+        switch (NVc) {
+            case 1: return da_decode_launch<T, 4, 1>(p, ntiles, st);
+            case 2: return da_decode_launch<T, 4, 2>(p, ntiles, st);
+            case 4: return da_decode_launch<T, 4, 4>(p, ntiles, st);
+            default: return da_decode_launch<T, 4, 8>(p, ntiles, st);
+        }
+    }
+    switch (NVc) {
+        case 1: return da_decode_launch<T, 8, 1>(p, ntiles, st);
+        case 2: return da_decode_launch<T, 8, 2>(p, ntiles, st);
+        case 4: return da_decode_launch<T, 8, 4>(p, ntiles, st);
+        default: return PA_ERR_UNSUPPORTED;
+    }
+}
+
 template <typename T, int NV>
 static int da_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
     int hpg = p.heads / p.num_kv_heads;
@@ -352,8 +614,8 @@ PA_API int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const
                              const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
                              int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
                              float scale, float temp_coef, int temp_every, float lambda, float out_mult, float eps,
-                             void* d_out, int elem, int nsplit, void* d_workspace, size_t workspace_bytes,
-                             pa_stream_t stream) {
+                             void* d_out, int elem, int nsplit, int single_token_tiles, void* d_workspace,
+                             size_t workspace_bytes, pa_stream_t stream) {
     PA_CHECK_ARG(d_q && d_k_pool && d_v_pool && d_table && d_q_tiles && d_out && num_q_tiles >= 0);
     PA_CHECK_ARG(num_slots > 0 && num_kv_heads > 0 && num_tiles > 0 && total_pages > 0 && tile_size > 0);
     PA_CHECK_ARG(heads > 0 && heads % num_kv_heads == 0 && dim > 0 && vdim > 0 && temp_every > 0);
@@ -367,7 +629,12 @@ PA_API int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const
     p.tile_size = tile_size; p.tiles = d_q_tiles; p.heads = heads; p.dim = dim; p.vdim = vdim; p.scale = scale;
     p.temp_coef = temp_coef; p.temp_every = temp_every; p.lambda = lambda; p.out_mult = out_mult; p.eps = eps;
     p.out = d_out; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace);
+    if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
+    if (single_token_tiles) {   // every tile is one token: the streaming kernel, where it serves the shape
+        const int st = elem == 4 ? da_decode_dispatch<float>(p, num_q_tiles, as_stream(stream))
+                                 : da_decode_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
+        if (st != PA_ERR_UNSUPPORTED) return st;
+    }
     if (elem == 4) return da_dispatch<float>(p, num_q_tiles, as_stream(stream));
-    if (elem == 2) return da_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
-    return PA_ERR_UNSUPPORTED;
+    return da_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
 }

@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t* __restric
 }
 
 // ---- grouped product ------------------------------------------------------------------------------------------------
-constexpr int kGlBM = 32, kGlBN = 64, kGlBK = 32;
+constexpr int kGlBM = 64, kGlBN = 64, kGlBK = 32;   // kGlBM is also the row tile of the tensor-core kernel
 
 // MODE 0: A rows gathered from the token rows (order[i] / top), scaled by a_scale[order[i]]; W[e] = [2 * n_out][K]
 //         (gate rows, then up rows); out[i][n] = silu(gate) * up in the activation type, sorted order.
@@ -150,10 +150,11 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
         src_row[r] = sr;
         src_scale[r] = sc;
     }
-    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;   // rows ty*2 .. +1, columns tx*4 .. +3
-    float acc[2][4], accu[2][4];
+    constexpr int RT = kGlBM / 16;                            // rows per thread
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;   // rows ty*RT .. +RT-1, columns tx*4 .. +3
+    float acc[RT][4], accu[RT][4];
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
+    for (int a = 0; a < RT; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) acc[a][b] = accu[a][b] = 0.f;
     for (int k0 = 0; k0 < K; k0 += kGlBK) {
@@ -181,23 +182,22 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
         __syncthreads();
 #pragma unroll 8
         for (int kk = 0; kk < kGlBK; ++kk) {
-            const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const float w = Bs[kk][tx * 4 + b];
-                acc[0][b] = fmaf(a0, w, acc[0][b]);
-                acc[1][b] = fmaf(a1, w, acc[1][b]);
-                if (MODE == 0) {
-                    const float u = Bu[kk][tx * 4 + b];
-                    accu[0][b] = fmaf(a0, u, accu[0][b]);
-                    accu[1][b] = fmaf(a1, u, accu[1][b]);
+                const float u = MODE == 0 ? Bu[kk][tx * 4 + b] : 0.f;
+#pragma unroll
+                for (int a = 0; a < RT; ++a) {
+                    const float av = As[kk][ty * RT + a];
+                    acc[a][b] = fmaf(av, w, acc[a][b]);
+                    if (MODE == 0) accu[a][b] = fmaf(av, u, accu[a][b]);
                 }
             }
         }
     }
 #pragma unroll
-    for (int a = 0; a < 2; ++a) {
-        const int r = ty * 2 + a;
+    for (int a = 0; a < RT; ++a) {
+        const int r = ty * RT + a;
         if (r >= nr) continue;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
@@ -212,6 +212,173 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
             }
         }
     }
+}
+
+// ---- the same product on the tensor cores (bfloat16 operands, float accumulation) -------------------------------------
+// CTA = 4 warps on a 64-row x 128-weight-row tile, K in steps of 32 through two shared-memory buffers (global loads of
+// step k + 1 are in flight while step k is multiplied).  MODE 0: weight rows [n0, n0 + 64) (gate) and the matching up
+// rows, so a thread holds gate and up of the same output and applies silu(gate) * up itself; MODE 1: 128 output columns.
+// Operands reach the mma.sync.m16n8k16 fragments through ldmatrix from rows padded to 80 bytes (conflict-free).
+// Needs K % 8 == 0 and 16-byte aligned rows (the dispatcher falls back to the kernel above otherwise).
+constexpr int kMmBK = 32, kMmLd = 40, kMmBRows = 128;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float sc) {
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        p[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+    return v;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restrict__ A, int64_t lda,
+                                                          const bf16_t* __restrict__ W, int K, int n_out,
+                                                          const int32_t* __restrict__ order,
+                                                          const float* __restrict__ a_scale, int top,
+                                                          const int32_t* __restrict__ tiles, bf16_t* __restrict__ out,
+                                                          float* __restrict__ out_f32) {
+    __shared__ __align__(16) bf16_t As[2][kGlBM][kMmLd];
+    __shared__ __align__(16) bf16_t Bs[2][kMmBRows][kMmLd];
+    __shared__ int src_row[kGlBM];
+    __shared__ float src_scale[kGlBM];
+    const int e = tiles[3 * blockIdx.x];
+    if (e < 0) return;
+    const int i0 = tiles[3 * blockIdx.x + 1], nr = tiles[3 * blockIdx.x + 2];
+    constexpr int NCOL = MODE == 0 ? 64 : 128;                     // outputs per CTA
+    const int n0 = blockIdx.y * NCOL;
+    const int w_rows = MODE == 0 ? 2 * n_out : n_out;
+    const bf16_t* We = W + (int64_t)e * w_rows * K;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < kGlBM) {
+        int sr = -1;
+        float sc = 1.f;
+        if (tid < nr) {
+            const int pair = order[i0 + tid];
+            if (MODE == 0) {
+                sr = pair / top;
+                if (a_scale) sc = a_scale[pair];
+            } else {
+                sr = i0 + tid;
+            }
+        }
+        src_row[tid] = sr;
+        src_scale[tid] = sc;
+    }
+    __syncthreads();
+    // loaders: A tile 64 rows x 4 vectors of 8 -> 2 per thread; B tile 128 rows x 4 vectors -> 4 per thread
+    const int lv = tid & 3;                                        // vector (8 elements) within the K step
+    uint4 ra[2], rb[4];
+    auto load_regs = [&](int k0) {
+        const int k = k0 + lv * 8;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int r = (tid >> 2) + j * 32;
+            const int sr = src_row[r];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (sr >= 0 && k < K) {
+                v = *reinterpret_cast<const uint4*>(A + (int64_t)sr * lda + k);
+                if (MODE == 0 && a_scale) v = scale_bf16x8(v, src_scale[r]);
+            }
+            ra[j] = v;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = (tid >> 2) + j * 32;                    // tile row 0..127
+            int wr;                                               // weight row
+            if (MODE == 0) wr = r < 64 ? n0 + r : n_out + n0 + (r - 64);
+            else wr = n0 + r;
+            const bool ok = (MODE == 0 ? (r < 64 ? n0 + r : n0 + r - 64) : n0 + r) < n_out && k < K;
+            rb[j] = ok ? *reinterpret_cast<const uint4*>(We + (int64_t)wr * K + k) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto store_regs = [&](int buf) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) *reinterpret_cast<uint4*>(&As[buf][(tid >> 2) + j * 32][lv * 8]) = ra[j];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(&Bs[buf][(tid >> 2) + j * 32][lv * 8]) = rb[j];
+    };
+    const int wm = warp & 1, wn = warp >> 1;                       // 32 rows x (MODE 0: 32 gate + 32 up | MODE 1: 64 columns)
+    float acc[2][8][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+    load_regs(0);
+    store_regs(0);
+    __syncthreads();
+    const int nk = (K + kMmBK - 1) / kMmBK;
+    for (int kt = 0; kt < nk; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) load_regs((kt + 1) * kMmBK);
+#pragma unroll
+        for (int ks = 0; ks < kMmBK; ks += 16) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+                ldsm_x4(smem_u32(&As[buf][wm * 32 + a * 16 + (lane & 15)][ks + (lane >> 4) * 8]), af[a][0], af[a][1], af[a][2], af[a][3]);
+#pragma unroll
+            for (int bp = 0; bp < 4; ++bp) {                      // pairs of 8-column tiles
+                int brow;
+                if (MODE == 0) brow = (bp < 2 ? 0 : 64) + wn * 32 + (bp & 1) * 16;
+                else brow = wn * 64 + bp * 16;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(&Bs[buf][brow + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    mma_bf16_16816(acc[a][bp * 2], af[a], b0, b1);
+                    mma_bf16_16816(acc[a][bp * 2 + 1], af[a], b2, b3);
+                }
+            }
+        }
+        if (kt + 1 < nk) store_regs(buf ^ 1);
+        __syncthreads();
+    }
+    // epilogue: c0,c1 -> row lane/4, columns 2*(lane%4) + {0,1}; c2,c3 -> row + 8
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int r = wm * 32 + a * 16 + hrow * 8 + (lane >> 2);
+            if (r >= nr) continue;
+            if (MODE == 0) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn * 32 + t * 8 + 2 * (lane & 3) + c;
+                        if (n >= n_out) continue;
+                        const float gte = __bfloat162float(__float2bfloat16_rn(acc[a][t][hrow * 2 + c]));
+                        const float up = __bfloat162float(__float2bfloat16_rn(acc[a][t + 4][hrow * 2 + c]));
+                        out[(int64_t)(i0 + r) * n_out + n] = __float2bfloat16_rn(silu_f32(gte) * up);
+                    }
+            } else {
+                float* dst = out_f32 + (int64_t)order[i0 + r] * n_out;
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn * 64 + t * 8 + 2 * (lane & 3) + c;
+                        if (n < n_out) dst[n] = acc[a][t][hrow * 2 + c];
+                    }
+            }
+        }
+}
+
+static bool mma_ok(const void* A, int64_t lda, const void* W, int K) {
+    return K % 8 == 0 && lda % 8 == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0;
 }
 
 }  // namespace pa
@@ -260,6 +427,12 @@ PA_API int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up,
     if (pairs <= 0) return PA_OK;
     dim3 grid((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((ff + kGlBN - 1) / kGlBN));
     const int32_t* tiles = d_meta + experts + 1;
+    if (elem == 2 && mma_ok(d_h, ldh, d_w_gate_up, width)) {
+        grouped_mma_kernel<0><<<grid, 128, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_gate_up), width, ff, d_order, d_sel_w, top,
+            tiles, static_cast<bf16_t*>(d_act), nullptr);
+        PA_RETURN_LAUNCH_STATUS();
+    }
     PA_DISPATCH_ELEM(elem, grouped_linear_kernel<T, 0><<<grid, 256, 0, as_stream(stream)>>>(
                                static_cast<const T*>(d_h), ldh, static_cast<const T*>(d_w_gate_up), width, ff, d_order,
                                d_sel_w, top, tiles, static_cast<T*>(d_act), nullptr));
@@ -272,6 +445,13 @@ PA_API int pa_moe_down(const void* d_act, const void* d_w_down, int ff, int widt
     if (pairs <= 0) return PA_OK;
     dim3 grid((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + kGlBN - 1) / kGlBN));
     const int32_t* tiles = d_meta + experts + 1;
+    if (elem == 2 && mma_ok(d_act, ff, d_w_down, ff)) {
+        dim3 g2((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + 127) / 128));
+        grouped_mma_kernel<1><<<g2, 128, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_act), (int64_t)ff, static_cast<const bf16_t*>(d_w_down), ff, width, d_order, nullptr, 1,
+            tiles, nullptr, d_out_pairs);
+        PA_RETURN_LAUNCH_STATUS();
+    }
     PA_DISPATCH_ELEM(elem, grouped_linear_kernel<T, 1><<<grid, 256, 0, as_stream(stream)>>>(
                                static_cast<const T*>(d_act), (int64_t)ff, static_cast<const T*>(d_w_down), ff, width,
                                d_order, nullptr, 1, tiles, nullptr, d_out_pairs));

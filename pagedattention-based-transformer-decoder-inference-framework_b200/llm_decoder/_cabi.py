@@ -116,7 +116,7 @@ _SIGS = {
     "pa_diff_attention_tile_tokens": ([_i32, _i32], _i32),
     "pa_diff_attention_workspace_bytes": ([_i32, _i32, _i32, _i32, _i32], _sz),
     "pa_diff_attention": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
-                           _f32, _f32, _i32, _f32, _f32, _f32, _vp, _i32, _i32, _vp, _sz, _vp], _i32),
+                           _f32, _f32, _i32, _f32, _f32, _f32, _vp, _i32, _i32, _i32, _vp, _sz, _vp], _i32),
     "pa_router_topk": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp], _i32),
     "pa_moe_tile_rows": ([], _i32),
     "pa_moe_max_tiles": ([_i32, _i32], _i32),

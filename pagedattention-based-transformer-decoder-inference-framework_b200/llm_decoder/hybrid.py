@@ -115,24 +115,29 @@ class DiffAttentionMixer:
         b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
         qkv = c.model._linear(hs, self.w_qkv)
         kv.append_rows(qkv, self.q_cols, self.q_cols + self.k_cols, b.row_slot, b.row_pos)
-        tiles, ntiles, longest = b.query_tiles(self.tile_tokens)
         out = c.empty(c.R, self.heads * self.vdim)
-        # few CTAs over a long context: cut the keys so the chip is filled (32 keys per step, >= 8 steps per part)
-        ctas = ntiles * self.kv_heads * max(1, math.ceil(self.heads // self.kv_heads / 32))
-        nsplit = 1
-        if ctas < 2 * c.model.sm_count and longest > 512:
-            nsplit = max(1, min(2 * c.model.sm_count // ctas, longest // 256, 64))
-        ws = None
-        if nsplit > 1:
-            ws = c.empty(lib.pa_diff_attention_workspace_bytes(ntiles, self.heads, self.kv_heads, self.vdim, nsplit),
-                         dtype=torch.uint8)
         pt = kv.page_table_
-        _chk(lib.pa_diff_attention(qkv.data_ptr(), qkv.stride(0), 0, kv.key_buffer_.data_ptr(), kv.value_buffer_.data_ptr(),
-                                   pt.device_data().data_ptr(), pt.num_beams_, pt.num_heads_, pt.num_tiles_,
-                                   kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, self.heads, self.dim,
-                                   self.vdim, self.scale, self.temp_coef, self.temp_every, self.lam, 1.0 - self.diff,
-                                   c.model.eps, out.data_ptr(), c.elem, nsplit, _cabi.ptr(ws),
-                                   ws.numel() if ws is not None else 0, s), "pa_diff_attention")
+        table = pt.device_data()
+        sms = c.model.sm_count
+        for single, group in zip((1, 0), b.query_tiles(self.tile_tokens)):
+            if group is None:
+                continue
+            tiles, ntiles, longest = group
+            # too few CTAs for the chip over a long context: cut the keys (at least 256 per part)
+            ctas = ntiles * self.kv_heads * max(1, math.ceil(self.heads // self.kv_heads / 32))
+            nsplit = 1
+            if ctas < 4 * sms and longest > 512:
+                nsplit = max(1, min(math.ceil(4 * sms / ctas), longest // 256, 64))
+            ws = None
+            if nsplit > 1:
+                ws = c.empty(lib.pa_diff_attention_workspace_bytes(ntiles, self.heads, self.kv_heads, self.vdim, nsplit),
+                             dtype=torch.uint8)
+            _chk(lib.pa_diff_attention(qkv.data_ptr(), qkv.stride(0), 0, kv.key_buffer_.data_ptr(),
+                                       kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
+                                       pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, self.heads,
+                                       self.dim, self.vdim, self.scale, self.temp_coef, self.temp_every, self.lam,
+                                       1.0 - self.diff, c.model.eps, out.data_ptr(), c.elem, nsplit, single, _cabi.ptr(ws),
+                                       ws.numel() if ws is not None else 0, s), "pa_diff_attention")
         return c.model._linear(out, self.w_o)
 
 

@@ -32,19 +32,25 @@ class RaggedBatch:
         self._cache = {}
 
     def query_tiles(self, tile_tokens):
-        """[n, 4] int32 (first row, tokens, slot, first position): every portion cut into runs of at most `tile_tokens`
-        tokens -- the work list of the attention kernel.  Also returns the longest context among the tiles."""
+        """The work lists of the attention kernels: every portion cut into runs of at most `tile_tokens` tokens, as
+        [n, 4] int32 device tensors (first row, tokens, slot, first position).  Two lists: portions of ONE token (decoded
+        tokens: the streaming kernel) and the rest.  Each comes as (tensor, count, longest context) or None."""
         key = ("qt", tile_tokens)
         if key not in self._cache:
-            tiles, longest = [], 0
+            groups = {True: [], False: []}
             for r0, n, slot, p0 in self.portions:
                 for o in range(0, n, tile_tokens):
-                    m = min(tile_tokens, n - o)
-                    tiles.append((r0 + o, m, slot, p0 + o))
-                    longest = max(longest, p0 + o + m)
-            t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4)
-            self._cache[key] = (t.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else t,
-                                len(tiles), longest)
+                    groups[n == 1].append((r0 + o, min(tile_tokens, n - o), slot, p0 + o))
+            out = []
+            for single in (True, False):
+                tiles = groups[single]
+                if not tiles:
+                    out.append(None)
+                    continue
+                t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4)
+                t = t.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else t
+                out.append((t, len(tiles), max(p + m for _r, m, _s, p in tiles)))
+            self._cache[key] = tuple(out)
         return self._cache[key]
 
     def scan_chunks(self, chunk):
