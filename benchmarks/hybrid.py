@@ -216,12 +216,12 @@ def bench_kernels(s, dev):
         kv.key_buffer_.normal_()
         kv.value_buffer_.normal_()
         tt = lib.pa_diff_attention_tile_tokens(H, G)
-        single = 1 if plen == 1 else 0
-        tiles, ntiles, longest = b.query_tiles(tt)[0 if single else 1]
+        single = 1 if plen == 1 else 2
+        tiles, ntiles, longest = b.query_tiles(tt, lib.pa_diff_attention_mma_tile_tokens(D, V, 2), 16)[single]
         o = torch.empty(R, H * V, device=dev, dtype=bf)
         ctas = ntiles * G
         nsplit = 1
-        if ctas < 4 * 148 and longest > 512:
+        if single == 1 and ctas < 4 * 148 and longest > 512:
             nsplit = max(1, min(math.ceil(4 * 148 / ctas), longest // 256, 64))
         wsb = lib.pa_diff_attention_workspace_bytes(ntiles, H, G, V, nsplit)
         ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)

@@ -589,15 +589,19 @@ int pa_kv_append_rows(void* d_k_pool, void* d_v_pool, const int32_t* d_table, in
  * causal, over the paged pools.  d_q_tiles [num_q_tiles][4] = (first row, tokens, slot, first position): runs of
  * at most pa_diff_attention_tile_tokens(heads, kv_heads) consecutive tokens of one portion.  nsplit > 1 cuts
  * the keys of every tile into that many parts (workspace: pa_diff_attention_workspace_bytes).
- * single_token_tiles != 0 promises that every tile holds ONE token (decode): those run on a kernel that streams
- * the keys straight from the pools, 8 warps across each tile's context. */
+ * tile_kind 0: the float tile kernel (any shape, both element types).  tile_kind 1 promises that every tile holds ONE
+ * token (decode): those run on a kernel that streams the keys straight from the pools, 8 warps across each tile's
+ * context.  tile_kind 2: bfloat16 only, tiles of up to pa_diff_attention_mma_tile_tokens(dim, vdim, elem) tokens
+ * (0 = this shape is not served) on the tensor cores, one query head per CTA, nsplit = 1; PA_ERR_UNSUPPORTED if the
+ * shape or an alignment (16-byte q rows and pools) rules it out. */
 int pa_diff_attention_tile_tokens(int heads, int kv_heads);
+int pa_diff_attention_mma_tile_tokens(int dim, int vdim, int elem);
 size_t pa_diff_attention_workspace_bytes(int num_q_tiles, int heads, int kv_heads, int vdim, int nsplit);
 int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
                       const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
                       int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
                       float scale, float temp_coef, int temp_every, float lambda, float out_mult, float eps,
-                      void* d_out, int elem, int nsplit, int single_token_tiles, void* d_workspace,
+                      void* d_out, int elem, int nsplit, int tile_kind, void* d_workspace,
                       size_t workspace_bytes, pa_stream_t stream);
 
 /* Router: float logits h . w_router[e], score_fn 0 = sigmoid / 1 = softmax, the `top` largest (ties: lower id),

@@ -579,6 +579,233 @@ static int da_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
     }
 }
 
+// ---- prompt portions on the tensor cores (bfloat16) -------------------------------------------------------------------
+// One CTA = up to 64 consecutive tokens of one portion x ONE query head; 8 warps: warp w owns the 16 rows (w & 3) of
+// map (w >> 2), so each map is a flash-attention of its own (mma.sync m16n8k16, bfloat16 operands, float accumulators)
+// over the SAME staged key and value tiles: 64 keys per step, located through the page table and brought in with
+// 16-byte cp.async copies into two buffers (the copies of step t + 1 fly while step t is multiplied).  Rows are padded
+// by 16 bytes so that ldmatrix reads are conflict-free.  The dot products are raw q . k; the position-dependent query
+// temperature and the scale multiply the float score (same product, no second rounding of q).  Scores, the running
+// maximum, the exponentials and their sum are float; the weights enter the second product rounded to bfloat16, like
+// every other matrix operand of this precision.  At the end the warps of map 2 leave a2 in shared memory and the warps
+// of map 1 take the difference, the head-wise norm and the output factor.
+constexpr int kDmRows = 64, kDmKeys = 64, kDmThreads = 256, kDmPad = 8;
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const DiffAttnParams p) {
+    constexpr int KD = 2 * DIM, KS = KD + kDmPad, VS = VDIM + kDmPad, NT = VDIM / 8;
+    extern __shared__ __align__(16) unsigned char dm_smem[];
+    bf16_t* Qs = reinterpret_cast<bf16_t*>(dm_smem);        // [64][KS]
+    bf16_t* Ks = Qs + kDmRows * KS;                          // [2][64][KS]
+    bf16_t* Vs = Ks + 2 * kDmKeys * KS;                      // [2][64][VS]
+    __shared__ int key_ok[2][kDmKeys];
+
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], ntok = tile[1], slot = tile[2], pos0 = tile[3];
+    const int h = blockIdx.y, g = h / (p.heads / p.num_kv_heads);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rg = warp & 3, map = warp >> 2;
+    const bf16_t* kp = static_cast<const bf16_t*>(p.k_pool);
+    const bf16_t* vp = static_cast<const bf16_t*>(p.v_pool);
+    const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
+    const int total = pos0 + ntok;                           // keys any row of the tile may see
+    const int nkt = (total + kDmKeys - 1) / kDmKeys;
+
+    for (int c = tid; c < kDmRows * (KD / 8); c += kDmThreads) {
+        const int r = c / (KD / 8), v = c % (KD / 8);
+        const bool ok = r < ntok;
+        const bf16_t* src = static_cast<const bf16_t*>(p.q) +
+                            (ok ? (int64_t)(row0 + r) * p.q_stride + p.q_off + (int64_t)h * KD + v * 8 : 0);
+        cp_async_16(smem_u32(Qs + r * KS + v * 8), src, ok);
+    }
+    auto pool_row = [&](int j) -> int64_t {
+        if (j < total && j / p.tile_size < p.num_tiles) {
+            const int page = trow[j / p.tile_size];
+            if (page >= 0 && page < p.total_pages) return (int64_t)page * p.tile_size + j % p.tile_size;
+        }
+        return -1;
+    };
+    auto load_tile = [&](int kt, int buf) {
+        const int c0 = kt * kDmKeys;
+        for (int c = tid; c < kDmKeys * (KD / 8); c += kDmThreads) {
+            const int key = c / (KD / 8), v = c % (KD / 8);
+            const int64_t pr = pool_row(c0 + key);
+            cp_async_16(smem_u32(Ks + (buf * kDmKeys + key) * KS + v * 8), kp + (pr >= 0 ? pr * KD + v * 8 : 0), pr >= 0);
+            if (v == 0) key_ok[buf][key] = pr >= 0;
+        }
+        for (int c = tid; c < kDmKeys * (VDIM / 8); c += kDmThreads) {
+            const int key = c / (VDIM / 8), v = c % (VDIM / 8);
+            const int64_t pr = pool_row(c0 + key);
+            cp_async_16(smem_u32(Vs + (buf * kDmKeys + key) * VS + v * 8), vp + (pr >= 0 ? pr * VDIM + v * 8 : 0), pr >= 0);
+        }
+    };
+    load_tile(0, 0);
+    cp_async_commit();
+
+    float o[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[t][c] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int rpos[2];
+    float sc[2];                                             // scale * temperature * log2(e) of the thread's two rows
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        rpos[i] = pos0 + rg * 16 + (lane >> 2) + 8 * i;
+        sc[i] = p.scale * (1.0f + p.temp_coef * logf((float)((rpos[i] + 1) / p.temp_every) + 1.0f)) * 1.4426950408889634f;
+    }
+
+    for (int kt = 0; kt < nkt; ++kt) {
+        const int buf = kt & 1, c0 = kt * kDmKeys;
+        if (kt + 1 < nkt) load_tile(kt + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        float s[8][4];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[t][c] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < DIM; ks += 16) {
+            uint32_t a[4];
+            ldsm_x4(smem_u32(Qs + (rg * 16 + (lane & 15)) * KS + map * DIM + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(Ks + (buf * kDmKeys + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + map * DIM + ks +
+                                 ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+                mma_bf16_16816(s[2 * np], a, b0, b1);
+                mma_bf16_16816(s[2 * np + 1], a, b2, b3);
+            }
+        }
+        // ---- float scores -> weights (log2 domain)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            const int col = t * 8 + 2 * (lane & 3);
+            const int2 okk = *reinterpret_cast<const int2*>(&key_ok[buf][col]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int i = c >> 1;
+                const bool vis = ((c & 1) ? okk.y : okk.x) && c0 + col + (c & 1) <= rpos[i];
+                s[t][c] = vis ? s[t][c] * sc[i] : -INFINITY;
+                mx[i] = fmaxf(mx[i], s[t][c]);
+            }
+        }
+        float ref[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float mn = fmaxf(m[i], mx[i]);
+            ref[i] = mn == -INFINITY ? 0.f : mn;
+            const float corr = exp2f(m[i] - ref[i]);         // m = -inf: 0 (nothing accumulated yet)
+            m[i] = mn;
+            l[i] *= corr;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                o[t][2 * i] *= corr;
+                o[t][2 * i + 1] *= corr;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                s[t][c] = exp2f(s[t][c] - ref[c >> 1]);
+                l[c >> 1] += s[t][c];
+            }
+        // ---- weighted sums
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(smem_u32(Vs + (buf * kDmKeys + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 +
+                                       (lane >> 4) * 8), b0, b1, b2, b3);
+                mma_bf16_16816(o[2 * np], a, b0, b1);
+                mma_bf16_16816(o[2 * np + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();                                     // this buffer is free for the copies of step kt + 2
+    }
+    cp_async_wait<0>();
+    // ---- a2 through shared memory, then difference, head-wise norm, output factor
+    float* A2 = reinterpret_cast<float*>(Ks);                // [64][VDIM] over the key / value buffers
+    float inv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        inv[i] = 1.0f / l[i];
+    }
+    if (map == 1) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                A2[(rg * 16 + (lane >> 2) + 8 * (c >> 1)) * VDIM + t * 8 + 2 * (lane & 3) + (c & 1)] = o[t][c] * inv[c >> 1];
+    }
+    __syncthreads();
+    if (map == 0) {
+        float ss[2] = {0.f, 0.f};
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float a2 = A2[(rg * 16 + (lane >> 2) + 8 * (c >> 1)) * VDIM + t * 8 + 2 * (lane & 3) + (c & 1)];
+                o[t][c] = o[t][c] * inv[c >> 1] - p.lambda * a2;
+                ss[c >> 1] = fmaf(o[t][c], o[t][c], ss[c >> 1]);
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 1);
+            ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 2);
+            const int r = rg * 16 + (lane >> 2) + 8 * i;
+            if (r >= ntok) continue;
+            const float f = p.out_mult / sqrtf(ss[i] / (float)VDIM + p.eps);
+            bf16_t* dst = static_cast<bf16_t*>(p.out) + (int64_t)(row0 + r) * p.heads * VDIM + (int64_t)h * VDIM + 2 * (lane & 3);
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+                *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16x2(o[t][2 * i] * f, o[t][2 * i + 1] * f);
+        }
+    }
+}
+
+template <int DIM, int VDIM>
+static int dm_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    const size_t smem = ((size_t)3 * kDmRows * (2 * DIM + kDmPad) + (size_t)2 * kDmKeys * (VDIM + kDmPad)) * sizeof(bf16_t);
+    auto kern = diff_attention_mma_kernel<DIM, VDIM>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((unsigned)ntiles, (unsigned)p.heads);
+    kern<<<grid, kDmThreads, smem, st>>>(p);
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+static bool dm_shape_ok(int dim, int vdim) {
+    return (dim == 32 || dim == 64 || dim == 128) && (vdim == 32 || vdim == 64 || vdim == 128);
+}
+
+// PA_ERR_UNSUPPORTED: this shape or these pointers stay on the float kernel
+static int dm_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    if (!dm_shape_ok(p.dim, p.vdim) || p.q_stride % 8 || p.q_off % 8) return PA_ERR_UNSUPPORTED;
+    if ((uintptr_t)p.q % 16 || (uintptr_t)p.k_pool % 16 || (uintptr_t)p.v_pool % 16 || (uintptr_t)p.out % 4) return PA_ERR_UNSUPPORTED;
+#define PA_DM_CASE(D, V) if (p.dim == D && p.vdim == V) return dm_launch<D, V>(p, ntiles, st)
+    PA_DM_CASE(32, 32); PA_DM_CASE(32, 64); PA_DM_CASE(32, 128);
+    PA_DM_CASE(64, 32); PA_DM_CASE(64, 64); PA_DM_CASE(64, 128);
+    PA_DM_CASE(128, 32); PA_DM_CASE(128, 64); PA_DM_CASE(128, 128);
+#undef PA_DM_CASE
+    return PA_ERR_UNSUPPORTED;
+}
+
 }  // namespace pa
 
 using namespace pa;
@@ -604,6 +831,10 @@ PA_API int pa_diff_attention_tile_tokens(int heads, int kv_heads) {
     return kDaRows / (hpg < kDaRows ? hpg : kDaRows);
 }
 
+PA_API int pa_diff_attention_mma_tile_tokens(int dim, int vdim, int elem) {
+    return elem == 2 && dm_shape_ok(dim, vdim) ? kDmRows : 0;
+}
+
 PA_API size_t pa_diff_attention_workspace_bytes(int num_tiles_q, int heads, int kv_heads, int vdim, int nsplit) {
     if (nsplit <= 1 || num_tiles_q <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
     const int hpg = heads / kv_heads, hc = hpg < kDaRows ? hpg : kDaRows, nchunk = (hpg + hc - 1) / hc;
@@ -614,7 +845,7 @@ PA_API int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const
                              const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,
                              int tile_size, const int32_t* d_q_tiles, int num_q_tiles, int heads, int dim, int vdim,
                              float scale, float temp_coef, int temp_every, float lambda, float out_mult, float eps,
-                             void* d_out, int elem, int nsplit, int single_token_tiles, void* d_workspace,
+                             void* d_out, int elem, int nsplit, int tile_kind, void* d_workspace,
                              size_t workspace_bytes, pa_stream_t stream) {
     PA_CHECK_ARG(d_q && d_k_pool && d_v_pool && d_table && d_q_tiles && d_out && num_q_tiles >= 0);
     PA_CHECK_ARG(num_slots > 0 && num_kv_heads > 0 && num_tiles > 0 && total_pages > 0 && tile_size > 0);
@@ -630,7 +861,11 @@ PA_API int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const
     p.temp_coef = temp_coef; p.temp_every = temp_every; p.lambda = lambda; p.out_mult = out_mult; p.eps = eps;
     p.out = d_out; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace);
     if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
-    if (single_token_tiles) {   // every tile is one token: the streaming kernel, where it serves the shape
+    if (tile_kind == 2) {       // tiles of up to pa_diff_attention_mma_tile_tokens tokens on the tensor cores
+        if (elem != 2 || nsplit != 1) return PA_ERR_UNSUPPORTED;
+        return dm_dispatch(p, num_q_tiles, as_stream(stream));
+    }
+    if (tile_kind == 1) {       // every tile is one token: the streaming kernel, where it serves the shape
         const int st = elem == 4 ? da_decode_dispatch<float>(p, num_q_tiles, as_stream(stream))
                                  : da_decode_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
         if (st != PA_ERR_UNSUPPORTED) return st;

@@ -222,15 +222,6 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
 // Needs K % 8 == 0 and 16-byte aligned rows (the dispatcher falls back to the kernel above otherwise).
 constexpr int kMmBK = 32, kMmLd = 40, kMmBRows = 128;
 
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float sc) {
     __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll

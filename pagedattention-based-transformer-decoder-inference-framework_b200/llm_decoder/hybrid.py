@@ -37,6 +37,7 @@ _ELEM = {torch.float32: 4, torch.bfloat16: 2}
 _KV = {torch.float32: "f32", torch.bfloat16: "bf16"}
 SCAN_CHUNK = 64           # tokens per chunk of the chunked recurrent scan
 SCAN_CHUNKED_FROM = 256   # portions at least this long use it
+MMA_FROM = 16             # portions at least this long run their attention on the tensor cores (bfloat16)
 
 
 def _chk(st, what):
@@ -110,6 +111,8 @@ class DiffAttentionMixer:
         self.k_cols = self.kv_heads * 2 * self.dim
         self.kv = model.states.add_kv_layer(self.kv_heads, 2 * self.dim, self.vdim, _KV[model.act_dtype])
         self.tile_tokens = model._lib.pa_diff_attention_tile_tokens(self.heads, self.kv_heads)
+        # portions of MMA_FROM tokens and more: the tensor-core kernel, where it serves the shape (0 = it does not)
+        self.mma_tokens = model._lib.pa_diff_attention_mma_tile_tokens(self.dim, self.vdim, _ELEM[model.act_dtype])
 
     def forward(self, c, hs):
         b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
@@ -119,14 +122,14 @@ class DiffAttentionMixer:
         pt = kv.page_table_
         table = pt.device_data()
         sms = c.model.sm_count
-        for single, group in zip((1, 0), b.query_tiles(self.tile_tokens)):
+        for kind, group in b.query_tiles(self.tile_tokens, self.mma_tokens, MMA_FROM).items():
             if group is None:
                 continue
             tiles, ntiles, longest = group
             # too few CTAs for the chip over a long context: cut the keys (at least 256 per part)
             ctas = ntiles * self.kv_heads * max(1, math.ceil(self.heads // self.kv_heads / 32))
             nsplit = 1
-            if ctas < 4 * sms and longest > 512:
+            if kind != 2 and ctas < 4 * sms and longest > 512:
                 nsplit = max(1, min(math.ceil(4 * sms / ctas), longest // 256, 64))
             ws = None
             if nsplit > 1:
@@ -136,7 +139,7 @@ class DiffAttentionMixer:
                                        kv.value_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_heads_,
                                        pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, self.heads,
                                        self.dim, self.vdim, self.scale, self.temp_coef, self.temp_every, self.lam,
-                                       1.0 - self.diff, c.model.eps, out.data_ptr(), c.elem, nsplit, single, _cabi.ptr(ws),
+                                       1.0 - self.diff, c.model.eps, out.data_ptr(), c.elem, nsplit, kind, _cabi.ptr(ws),
                                        ws.numel() if ws is not None else 0, s), "pa_diff_attention")
         return c.model._linear(out, self.w_o)
 

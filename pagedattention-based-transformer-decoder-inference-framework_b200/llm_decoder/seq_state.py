@@ -31,26 +31,29 @@ class RaggedBatch:
         self.device = device
         self._cache = {}
 
-    def query_tiles(self, tile_tokens):
-        """The work lists of the attention kernels: every portion cut into runs of at most `tile_tokens` tokens, as
-        [n, 4] int32 device tensors (first row, tokens, slot, first position).  Two lists: portions of ONE token (decoded
-        tokens: the streaming kernel) and the rest.  Each comes as (tensor, count, longest context) or None."""
-        key = ("qt", tile_tokens)
+    def query_tiles(self, tile_tokens, big_tokens=0, big_from=0):
+        """The work lists of the attention kernels: every portion cut into runs of consecutive tokens, as [n, 4] int32
+        device tensors (first row, tokens, slot, first position).  Three lists, keyed by the kernel's tile kind:
+        1 = portions of ONE token (decoded tokens: the streaming kernel), 2 = portions of at least `big_from` tokens in
+        runs of `big_tokens` (the tensor-core kernel; none when big_tokens is 0), 0 = the rest in runs of `tile_tokens`.
+        Each comes as (tensor, count, longest context) or None."""
+        key = ("qt", tile_tokens, big_tokens, big_from)
         if key not in self._cache:
-            groups = {True: [], False: []}
+            groups = {0: [], 1: [], 2: []}
             for r0, n, slot, p0 in self.portions:
-                for o in range(0, n, tile_tokens):
-                    groups[n == 1].append((r0 + o, min(tile_tokens, n - o), slot, p0 + o))
-            out = []
-            for single in (True, False):
-                tiles = groups[single]
+                kind = 1 if n == 1 else 2 if big_tokens and n >= big_from else 0
+                step = big_tokens if kind == 2 else tile_tokens
+                for o in range(0, n, step):
+                    groups[kind].append((r0 + o, min(step, n - o), slot, p0 + o))
+            out = {}
+            for kind, tiles in groups.items():
                 if not tiles:
-                    out.append(None)
+                    out[kind] = None
                     continue
                 t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4)
                 t = t.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else t
-                out.append((t, len(tiles), max(p + m for _r, m, _s, p in tiles)))
-            self._cache[key] = tuple(out)
+                out[kind] = (t, len(tiles), max(p + m for _r, m, _s, p in tiles))
+            self._cache[key] = out
         return self._cache[key]
 
     def scan_chunks(self, chunk):

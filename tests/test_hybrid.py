@@ -484,3 +484,104 @@ def test_kernels_alone_against_the_oracle_functions():
                                 outp.data_ptr(), 4, s()), "down")
     got = outp.view(rows, top, wdt).double().sum(1).cpu()
     assert (got - want).abs().max() < 1e-4
+
+
+# ---- the tensor-core attention kernel (bfloat16 portions of 16 tokens and more) ---------------------------------------
+def _selector(rows, cols, first):
+    m = torch.zeros(rows, cols, dtype=torch.float64)
+    m[torch.arange(rows), first + torch.arange(rows)] = 1.0
+    return m
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,vdim,heads,kv_heads,tile_size", [(32, 64, 4, 2, 16), (64, 128, 3, 3, 16), (128, 32, 2, 1, 64),
+                                                               (64, 64, 6, 2, 8)])
+def test_tensor_core_attention_kernel_against_the_oracle(dim, vdim, heads, kv_heads, tile_size):
+    """pa_diff_attention, tile kind 2, called directly on bfloat16 rows with a peaked softmax (queries scaled up, so a
+    key too many or too few at a tile's, a page's or the causal edge moves a row by O(1)): one sequence fed as 150 + 100
+    tokens (the second portion starts in the middle of a key tile and of a page), one of 70 tokens from its first token
+    in the same launch, on pages that another sequence held before.  The oracle gets the same rounded q / k / v through
+    identity projections."""
+    from llm_decoder import _cabi
+    from llm_decoder.seq_state import SequenceStateCache
+    lib, dev = _cabi.lib(), torch.device("cuda")
+    assert lib.pa_diff_attention_mma_tile_tokens(dim, vdim, 2) == 64
+    assert lib.pa_diff_attention_mma_tile_tokens(dim, vdim, 4) == 0 and lib.pa_diff_attention_mma_tile_tokens(24, vdim, 2) == 0
+    qc, kc, vc = heads * 2 * dim, kv_heads * 2 * dim, kv_heads * vdim
+    cols = qc + kc + vc
+    scale, diff, coef, every, eps = 0.9 / math.sqrt(dim), 0.3, 0.4, 48, 1e-5
+    lq1, lk1 = torch.zeros(dim, dtype=torch.float64), torch.zeros(dim, dtype=torch.float64)
+    lq2, lk2 = lq1.clone(), lk1.clone()
+    lq1[0], lk1[0], lq2[1], lk2[1] = 0.2, 1.0, -0.1, 1.0
+    lam = math.exp(0.2) - math.exp(-0.1) + diff
+    g = torch.Generator().manual_seed(dim + vdim)
+    seqs = {"a": torch.randn(250, cols, generator=g), "b": torch.randn(70, cols, generator=g)}
+    for t in seqs.values():
+        t[:, :qc] *= 3.0
+    seqs = {k: v.to(torch.bfloat16) for k, v in seqs.items()}
+    states = SequenceStateCache(3, 512, tile_size, dev)
+    kv = states.add_kv_layer(kv_heads, 2 * dim, vdim, "bf16")
+    old = states.alloc()
+    states.extend(old, 40)
+    slot = {"a": states.alloc(), "b": states.alloc()}
+    states.free(old)
+    got = {k: [] for k in seqs}
+    fed = {k: 0 for k in seqs}
+    for step in ([("a", 150)], [("a", 100), ("b", 70)]):
+        batch = states.make_batch([(slot[k], [0] * n) for k, n in step])
+        qkv = torch.cat([seqs[k][fed[k]:fed[k] + n] for k, n in step]).to(dev).contiguous()
+        kv.append_rows(qkv, qc, qc + kc, batch.row_slot, batch.row_pos)
+        tiles, ntiles, _longest = batch.query_tiles(lib.pa_diff_attention_tile_tokens(heads, kv_heads), 64, 16)[2]
+        out = torch.zeros(batch.rows, heads * vdim, dtype=torch.bfloat16, device=dev)
+        pt = kv.page_table_
+        _cabi.check(lib.pa_diff_attention(qkv.data_ptr(), qkv.stride(0), 0, kv.key_buffer_.data_ptr(), kv.value_buffer_.data_ptr(),
+                                          pt.device_data().data_ptr(), pt.num_beams_, pt.num_heads_, pt.num_tiles_,
+                                          kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, heads, dim, vdim, scale, coef,
+                                          every, lam, 1.0 - diff, eps, out.data_ptr(), 2, 1, 2, None, 0, _cabi.stream()),
+                    "pa_diff_attention")
+        torch.cuda.synchronize()
+        r0 = 0
+        for k, n in step:
+            got[k].append(out[r0:r0 + n].double().cpu())
+            fed[k] += n
+            r0 += n
+    for k, rows in seqs.items():
+        want = R.diff_attention_mixer_fast(rows.double(), _selector(qc, cols, 0), _selector(kc, cols, qc), _selector(vc, cols, qc + kc),
+                                           torch.eye(heads * vdim, dtype=torch.float64), lq1, lk1, lq2, lk2, heads, kv_heads, dim,
+                                           vdim, scale, diff, coef, every, eps)
+        err = (torch.cat(got[k]) - want).abs().max().item()
+        assert err < 0.04, f"sequence {k}: max abs error {err}"
+
+
+def cfg_mma_heads():
+    # head sizes the tensor-core attention kernel serves in bfloat16
+    return R.make_config([R.attention_layer(heads=4, kv_heads=2, dim=32, vdim=64, coef=0.3, every=16, mlp=R.dense_mlp(64)),
+                          R.mingru_layer(48, None),
+                          R.attention_layer(heads=2, kv_heads=1, dim=64, vdim=32, diff=0.15, coef=0.2, every=50)],
+                         width=64, vocab=83, residual_mult=0.6)
+
+
+CONFIGS["mma_heads"] = cfg_mma_heads
+
+
+@pytest.mark.gpu
+def test_bfloat16_portions_on_the_tensor_cores_equal_small_portions():
+    """bfloat16, head sizes of the tensor-core kernel: a 230-token prompt in one step, in portions that switch between
+    the tensor-core kernel (16 tokens and more) and the float kernels (shorter, and single tokens), and batched beside
+    another request give the same logits up to rounding, and the oracle's."""
+    import llm_decoder as ld
+    config, W = _case("mma_heads")
+    toks = _tokens(230, config["vocab"], 51)
+    other = _tokens(90, config["vocab"], 52)
+    want = _oracle("mma_heads", config, W, toks)
+    whole = _feed(ld.Engine(_model(config, W, "bfloat16")), "a", toks, [])
+    _close(whole, want, "bfloat16")
+    cut = _feed(ld.Engine(_model(config, W, "bfloat16")), "a", toks, [3, 19, 35, 99, 100, 110, 174, 229])
+    eng = ld.Engine(_model(config, W, "bfloat16"))
+    outs = [eng.step([("a", toks[:64], list(range(64))), ("b", other[:17], [])])]
+    outs.append(eng.step([("b", other[17:], []), ("a", toks[64:65], [0])]))
+    outs.append(eng.step([("a", toks[65:], list(range(165)))]))
+    mixed = torch.cat(outs, 0)
+    for got in (cut, mixed):
+        rel = (got.double() - whole.double()).pow(2).mean(-1).sqrt() / whole.double().pow(2).mean(-1).sqrt()
+        assert rel.max().item() < 0.03, f"relative rms difference {rel.max().item()}"
