@@ -17,30 +17,84 @@ namespace pa {
 
 // ---- router ---------------------------------------------------------------------------------------------------------
 // One warp per row.  score_fn: 0 = sigmoid, 1 = softmax over the experts.  Ties go to the lower expert id.
+// The dot products run over groups of kRtGroup weight vectors (the experts' rows and, last, the shared-expert gate's):
+// a lane takes 16-byte pieces of the token row and multiplies each into the whole group, so the row is read once per
+// group and the weights with 16-byte loads (VEC; rows whose width or alignment does not allow it go element by element).
+constexpr int kRtGroup = 8;
+
 template <typename T>
+__device__ __forceinline__ void rt_load(const T* p, float (&f)[16 / sizeof(T)]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    if (sizeof(T) == 4) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+}
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
                                                           const float* __restrict__ w_shared_gate, int rows, int width,
                                                           int experts, int top, int score_fn, int renorm,
                                                           int32_t* __restrict__ sel_id, float* __restrict__ sel_w,
                                                           float* __restrict__ shared_gate) {
     extern __shared__ float sc[];                     // [warps][experts]
+    constexpr int VN = 16 / sizeof(T);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return;
     float* s = sc + warp * experts;
     const T* hr = h + (int64_t)row * width;
-    for (int e = 0; e < experts; ++e) {
-        const float* wr = w_router + (int64_t)e * width;
-        float acc = 0.f;
-        for (int j = lane; j < width; j += 32) acc = fmaf(to_f32<T>(hr[j]), wr[j], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
-    }
-    if (w_shared_gate) {
-        float acc = 0.f;
-        for (int j = lane; j < width; j += 32) acc = fmaf(to_f32<T>(hr[j]), w_shared_gate[j], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) shared_gate[row] = sigmoid_f32(acc);
+    const int nvec = experts + (w_shared_gate ? 1 : 0);
+    for (int e0 = 0; e0 < nvec; e0 += kRtGroup) {
+        float acc[kRtGroup];
+        const float* wr[kRtGroup];
+#pragma unroll
+        for (int c = 0; c < kRtGroup; ++c) {
+            acc[c] = 0.f;
+            const int e = e0 + c;
+            wr[c] = e < experts ? w_router + (int64_t)e * width : e < nvec ? w_shared_gate : nullptr;
+        }
+        if (VEC) {
+            for (int j = lane * VN; j < width; j += 32 * VN) {
+                float hv[VN];
+                rt_load<T>(hr + j, hv);
+#pragma unroll
+                for (int c = 0; c < kRtGroup; ++c) {
+                    if (!wr[c]) continue;
+#pragma unroll
+                    for (int i = 0; i < VN; i += 4) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(wr[c] + j + i);
+                        acc[c] = fmaf(hv[i], w4.x, acc[c]);
+                        acc[c] = fmaf(hv[i + 1], w4.y, acc[c]);
+                        acc[c] = fmaf(hv[i + 2], w4.z, acc[c]);
+                        acc[c] = fmaf(hv[i + 3], w4.w, acc[c]);
+                    }
+                }
+            }
+        } else {
+            for (int j = lane; j < width; j += 32) {
+                const float hv = to_f32<T>(hr[j]);
+#pragma unroll
+                for (int c = 0; c < kRtGroup; ++c)
+                    if (wr[c]) acc[c] = fmaf(hv, wr[c][j], acc[c]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < kRtGroup; ++c) {
+            const int e = e0 + c;
+            if (e >= nvec) continue;
+            const float v = warp_sum(acc[c]);
+            if (lane == 0) {
+                if (e < experts) s[e] = v;
+                else shared_gate[row] = sigmoid_f32(v);
+            }
+        }
     }
     __syncwarp();
     if (lane == 0) {
@@ -368,6 +422,135 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
         }
 }
 
+// ---- few rows per expert (decoding): the weights are the traffic -------------------------------------------------------
+// CTA = 4 warps on one row tile (up to 64 sorted pairs of one expert, in groups of 16) x 32 weight rows (MODE 0: 16 gate
+// rows and the matching 16 up rows; MODE 1: 32 output columns).  Nothing is staged: the warps split K into interleaved
+// pieces of 32, and a lane reads 16 bytes (8 consecutive k) of ITS weight row and of its two token rows straight into the
+// mma.sync.m16n8k16 fragments.  The sum over k does not care about order, so the 8 values a lane holds stand for k slots
+// {2t, 2t+1, 2t+8, 2t+9} of two consecutive MMAs -- the same assignment on both operands.  16 weight loads per lane are in
+// flight before the first MMA of a step; many small CTAs keep the whole chip's memory system busy with 16 rows a tile.
+// The warps' partial sums meet in shared memory.  Same argument rules as the kernel above.
+constexpr int kSkChunk = 32, kSkUnroll = 4, kSkWarps = 4, kSkCols = 32, kSkGroups = kGlBM / 16;
+
+template <int MODE>
+__global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf16_t* __restrict__ A, int64_t lda,
+                                                                       const bf16_t* __restrict__ W, int K, int n_out,
+                                                                       const int32_t* __restrict__ order,
+                                                                       const float* __restrict__ a_scale, int top,
+                                                                       const int32_t* __restrict__ tiles,
+                                                                       bf16_t* __restrict__ out, float* __restrict__ out_f32) {
+    __shared__ float red[kSkWarps][kGlBM][kSkCols + 1];
+    __shared__ int src_row[kGlBM];
+    __shared__ float src_scale[kGlBM];
+    const int e = tiles[3 * blockIdx.x];
+    if (e < 0) return;
+    const int i0 = tiles[3 * blockIdx.x + 1], nr = tiles[3 * blockIdx.x + 2];
+    constexpr int NCOL = MODE == 0 ? 16 : 32;                      // outputs per CTA
+    const int n0 = blockIdx.y * NCOL;
+    const int w_rows = MODE == 0 ? 2 * n_out : n_out;
+    const bf16_t* We = W + (int64_t)e * w_rows * K;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if (tid < kGlBM) {
+        int sr = -1;
+        float sc = 1.f;
+        if (tid < nr) {
+            const int pair = order[i0 + tid];
+            if (MODE == 0) {
+                sr = pair / top;
+                if (a_scale) sc = a_scale[pair];
+            } else {
+                sr = i0 + tid;
+            }
+        }
+        src_row[tid] = sr;
+        src_scale[tid] = sc;
+    }
+    __syncthreads();
+    const int ngroups = (nr + 15) / 16;
+    // this lane's weight row of each of the 4 column tiles (nullptr: past the end)
+    const bf16_t* wrow[4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        int col, wr;
+        if (MODE == 0) { col = n0 + (nt & 1) * 8 + g; wr = (nt < 2 ? 0 : n_out) + col; }
+        else { col = n0 + nt * 8 + g; wr = col; }
+        wrow[nt] = col < n_out ? We + (int64_t)wr * K : nullptr;
+    }
+    float acc[kSkGroups][4][4];
+#pragma unroll
+    for (int a = 0; a < kSkGroups; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int kc = warp * kSkChunk; kc < K; kc += kSkWarps * kSkChunk * kSkUnroll) {
+        uint4 wv[kSkUnroll][4];
+#pragma unroll
+        for (int u = 0; u < kSkUnroll; ++u) {
+            const int k = kc + u * kSkWarps * kSkChunk + 8 * t;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+                wv[u][nt] = (wrow[nt] && k < K) ? ldg_stream_128(wrow[nt] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kSkUnroll; ++u) {
+            const int k = kc + u * kSkWarps * kSkChunk + 8 * t;
+#pragma unroll
+            for (int mt = 0; mt < kSkGroups; ++mt) {
+                if (mt >= ngroups) break;
+                const int r0 = mt * 16 + g, r1 = r0 + 8;
+                uint4 x = zero, y = zero;
+                if (src_row[r0] >= 0 && k < K) {
+                    x = *reinterpret_cast<const uint4*>(A + (int64_t)src_row[r0] * lda + k);
+                    if (MODE == 0 && a_scale) x = scale_bf16x8(x, src_scale[r0]);
+                }
+                if (src_row[r1] >= 0 && k < K) {
+                    y = *reinterpret_cast<const uint4*>(A + (int64_t)src_row[r1] * lda + k);
+                    if (MODE == 0 && a_scale) y = scale_bf16x8(y, src_scale[r1]);
+                }
+                const uint32_t a_lo[4] = {x.x, y.x, x.y, y.y}, a_hi[4] = {x.z, y.z, x.w, y.w};
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    mma_bf16_16816(acc[mt][nt], a_lo, wv[u][nt].x, wv[u][nt].y);
+                    mma_bf16_16816(acc[mt][nt], a_hi, wv[u][nt].z, wv[u][nt].w);
+                }
+            }
+        }
+    }
+    // c0,c1 -> row g, columns 2t + {0,1} of the column tile; c2,c3 -> row g + 8
+#pragma unroll
+    for (int mt = 0; mt < kSkGroups; ++mt) {
+        if (mt >= ngroups) break;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                red[warp][mt * 16 + g + (c >> 1) * 8][nt * 8 + 2 * t + (c & 1)] = acc[mt][nt][c];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nr * NCOL; idx += kSkWarps * 32) {
+        const int r = idx / NCOL, c = idx % NCOL;
+        if (n0 + c >= n_out) continue;
+        if (MODE == 0) {
+            float gte = 0.f, up = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSkWarps; ++w) { gte += red[w][r][c]; up += red[w][r][16 + c]; }
+            gte = __bfloat162float(__float2bfloat16_rn(gte));
+            up = __bfloat162float(__float2bfloat16_rn(up));
+            out[(int64_t)(i0 + r) * n_out + n0 + c] = __float2bfloat16_rn(silu_f32(gte) * up);
+        } else {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSkWarps; ++w) v += red[w][r][c];
+            out_f32[(int64_t)order[i0 + r] * n_out + n0 + c] = v;
+        }
+    }
+}
+
+// few pairs per expert: the streaming form
+static bool skinny_ok(int pairs, int experts) { return pairs <= 32 * experts; }
+
 static bool mma_ok(const void* A, int64_t lda, const void* W, int K) {
     return K % 8 == 0 && lda % 8 == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0;
 }
@@ -384,9 +567,16 @@ PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float*
     if (rows == 0) return PA_OK;
     if (experts > 2048) return PA_ERR_UNSUPPORTED;
     const size_t smem = (size_t)4 * experts * sizeof(float);
-    PA_DISPATCH_ELEM(elem, router_topk_kernel<T><<<(unsigned)((rows + 3) / 4), 128, smem, as_stream(stream)>>>(
-                               static_cast<const T*>(d_h), d_w_router, d_w_shared_gate, rows, width, experts, top,
-                               score_fn, renorm, d_sel_id, d_sel_w, d_shared_gate));
+    // 16-byte pieces: every row of the tokens and of the float weight vectors must start on a 16-byte boundary
+    const bool vec = width % 8 == 0 && (uintptr_t)d_h % 16 == 0 && (uintptr_t)d_w_router % 16 == 0 &&
+                     (uintptr_t)d_w_shared_gate % 16 == 0;
+#define PA_ROUTER(VEC)                                                                                                 \
+    PA_DISPATCH_ELEM(elem, (router_topk_kernel<T, VEC><<<(unsigned)((rows + 3) / 4), 128, smem, as_stream(stream)>>>(  \
+                               static_cast<const T*>(d_h), d_w_router, d_w_shared_gate, rows, width, experts, top,     \
+                               score_fn, renorm, d_sel_id, d_sel_w, d_shared_gate)))
+    if (vec) PA_ROUTER(true);
+    else PA_ROUTER(false);
+#undef PA_ROUTER
     PA_RETURN_LAUNCH_STATUS();
 }
 
@@ -418,6 +608,13 @@ PA_API int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up,
     if (pairs <= 0) return PA_OK;
     dim3 grid((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((ff + kGlBN - 1) / kGlBN));
     const int32_t* tiles = d_meta + experts + 1;
+    if (elem == 2 && mma_ok(d_h, ldh, d_w_gate_up, width) && skinny_ok(pairs, experts)) {
+        dim3 gs((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((ff + 15) / 16));
+        grouped_skinny_kernel<0><<<gs, kSkWarps * 32, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_gate_up), width, ff, d_order, d_sel_w, top,
+            tiles, static_cast<bf16_t*>(d_act), nullptr);
+        PA_RETURN_LAUNCH_STATUS();
+    }
     if (elem == 2 && mma_ok(d_h, ldh, d_w_gate_up, width)) {
         grouped_mma_kernel<0><<<grid, 128, 0, as_stream(stream)>>>(
             static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_gate_up), width, ff, d_order, d_sel_w, top,
@@ -436,6 +633,13 @@ PA_API int pa_moe_down(const void* d_act, const void* d_w_down, int ff, int widt
     if (pairs <= 0) return PA_OK;
     dim3 grid((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + kGlBN - 1) / kGlBN));
     const int32_t* tiles = d_meta + experts + 1;
+    if (elem == 2 && mma_ok(d_act, ff, d_w_down, ff) && skinny_ok(pairs, experts)) {
+        dim3 gs((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + kSkCols - 1) / kSkCols));
+        grouped_skinny_kernel<1><<<gs, kSkWarps * 32, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_act), (int64_t)ff, static_cast<const bf16_t*>(d_w_down), ff, width, d_order, nullptr, 1,
+            tiles, nullptr, d_out_pairs);
+        PA_RETURN_LAUNCH_STATUS();
+    }
     if (elem == 2 && mma_ok(d_act, ff, d_w_down, ff)) {
         dim3 g2((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + 127) / 128));
         grouped_mma_kernel<1><<<g2, 128, 0, as_stream(stream)>>>(

@@ -86,41 +86,89 @@ __global__ void __launch_bounds__(256) rms_state_store_kernel(const float* __res
 
 // ---- minGRU ---------------------------------------------------------------------------------------------------------
 // zxg row layout: [z pre-activation | candidate pre-activation | output-gate pre-activation], each `width` wide.
-template <typename T>
-struct MinGruStep {
-    float a, b, gate;
-    __device__ __forceinline__ MinGruStep(const T* __restrict__ row, int width, int c, float zb, float xb) {
-        const float z = sigmoid_f32(to_f32<T>(row[c]) + zb);
-        const float u = to_f32<T>(row[width + c]) + xb;
-        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f32(u);
-        a = 1.0f - z;
-        b = z * cand;
-        gate = silu_f32(to_f32<T>(row[2 * width + c]));
+// A thread owns V adjacent channels (V = 2 where the width is even: one 4- or 8-byte load per row and field) and
+// walks its tokens in order; the loads of the next tokens do not depend on the state and are issued ahead (unrolled).
+template <typename T, int V> struct MinGruVec;
+template <typename T> struct MinGruVec<T, 1> {
+    static __device__ __forceinline__ void load(const T* p, float (&f)[1]) { f[0] = to_f32<T>(*p); }
+    static __device__ __forceinline__ void store(T* p, const float (&f)[1]) { *p = from_f32<T>(f[0]); }
+};
+template <> struct MinGruVec<float, 2> {
+    static __device__ __forceinline__ void load(const float* p, float (&f)[2]) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        f[0] = v.x; f[1] = v.y;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&f)[2]) { *reinterpret_cast<float2*>(p) = make_float2(f[0], f[1]); }
+};
+template <> struct MinGruVec<bf16_t, 2> {
+    static __device__ __forceinline__ void load(const bf16_t* p, float (&f)[2]) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+        f[0] = v.x; f[1] = v.y;
+    }
+    static __device__ __forceinline__ void store(bf16_t* p, const float (&f)[2]) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(f[0], f[1]);
     }
 };
 
-template <typename T>
+template <typename T, int V>
+struct MinGruStep {
+    float a[V], b[V], gate[V];
+    __device__ __forceinline__ MinGruStep(const T* __restrict__ row, int width, int c, const float (&zb)[V], const float (&xb)[V]) {
+        float zr[V], ur[V], gr[V];
+        MinGruVec<T, V>::load(row + c, zr);
+        MinGruVec<T, V>::load(row + width + c, ur);
+        MinGruVec<T, V>::load(row + 2 * width + c, gr);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float z = sigmoid_f32(zr[i] + zb[i]);
+            const float u = ur[i] + xb[i];
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f32(u);
+            a[i] = 1.0f - z;
+            b[i] = z * cand;
+            gate[i] = silu_f32(gr[i]);
+        }
+    }
+};
+
+template <int V>
+__device__ __forceinline__ void mingru_biases(const float* z_bias, const float* x_bias, int c, float (&zb)[V], float (&xb)[V]) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        zb[i] = z_bias ? z_bias[c + i] : 0.f;
+        xb[i] = x_bias ? x_bias[c + i] : 0.f;
+    }
+}
+
+template <typename T, int V>
 __global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ zxg, const float* __restrict__ z_bias,
                                                           const float* __restrict__ x_bias, int width,
                                                           const int32_t* __restrict__ seq_start,
                                                           const int32_t* __restrict__ seq_len,
                                                           const int32_t* __restrict__ seq_slot, float* __restrict__ state,
                                                           T* __restrict__ y) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     const int s = blockIdx.y;
     if (c >= width) return;
     const int n = seq_len[s];
     if (n <= 0) return;
     const int64_t r0 = seq_start[s];
-    const float zb = z_bias ? z_bias[c] : 0.f, xb = x_bias ? x_bias[c] : 0.f;
+    float zb[V], xb[V], S[V], o[V];
+    mingru_biases<V>(z_bias, x_bias, c, zb, xb);
     float* sp = state + (int64_t)seq_slot[s] * width + c;
-    float S = *sp;
+#pragma unroll
+    for (int i = 0; i < V; ++i) S[i] = sp[i];
+#pragma unroll 4
     for (int t = 0; t < n; ++t) {
-        const MinGruStep<T> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
-        S = st.a * S + st.b;
-        y[(r0 + t) * width + c] = from_f32<T>(S * st.gate);
+        const MinGruStep<T, V> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            S[i] = st.a[i] * S[i] + st.b[i];
+            o[i] = S[i] * st.gate[i];
+        }
+        MinGruVec<T, V>::store(y + (r0 + t) * width + c, o);
     }
-    *sp = S;
+#pragma unroll
+    for (int i = 0; i < V; ++i) sp[i] = S[i];
 }
 
 // Chunked scan for long portions.  A portion is cut into chunks of `chunk` tokens (chunk list built by the host:
@@ -128,26 +176,35 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const T* __restrict__ 
 // the pair (A, B) with S_out = A * S_in + B.  Pass 2: per (portion, channel) the chunk pairs are chained in order from
 // the state slot, leaving each chunk's S_in in place of its A and the new state in the slot.  Pass 3: every chunk
 // replays its tokens from S_in and writes the outputs.
-template <typename T>
+template <typename T, int V>
 __global__ void __launch_bounds__(128) mingru_chunk_fold_kernel(const T* __restrict__ zxg, const float* __restrict__ z_bias,
                                                                 const float* __restrict__ x_bias, int width,
                                                                 const int32_t* __restrict__ chunk_start,
                                                                 const int32_t* __restrict__ chunk_len,
                                                                 float* __restrict__ AB) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     const int k = blockIdx.y;
     if (c >= width) return;
     const int n = chunk_len[k];
     const int64_t r0 = chunk_start[k];
-    const float zb = z_bias ? z_bias[c] : 0.f, xb = x_bias ? x_bias[c] : 0.f;
-    float A = 1.f, B = 0.f;
+    float zb[V], xb[V], A[V], B[V];
+    mingru_biases<V>(z_bias, x_bias, c, zb, xb);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { A[i] = 1.f; B[i] = 0.f; }
+#pragma unroll 8
     for (int t = 0; t < n; ++t) {
-        const MinGruStep<T> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
-        A *= st.a;
-        B = st.a * B + st.b;
+        const MinGruStep<T, V> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            A[i] *= st.a[i];
+            B[i] = st.a[i] * B[i] + st.b[i];
+        }
     }
-    AB[((int64_t)k * 2) * width + c] = A;
-    AB[((int64_t)k * 2 + 1) * width + c] = B;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        AB[((int64_t)k * 2) * width + c + i] = A[i];
+        AB[((int64_t)k * 2 + 1) * width + c + i] = B[i];
+    }
 }
 
 __global__ void __launch_bounds__(128) mingru_chunk_chain_kernel(float* __restrict__ AB, int width,
@@ -171,23 +228,30 @@ __global__ void __launch_bounds__(128) mingru_chunk_chain_kernel(float* __restri
     *sp = S;
 }
 
-template <typename T>
+template <typename T, int V>
 __global__ void __launch_bounds__(128) mingru_chunk_apply_kernel(const T* __restrict__ zxg, const float* __restrict__ z_bias,
                                                                  const float* __restrict__ x_bias, int width,
                                                                  const int32_t* __restrict__ chunk_start,
                                                                  const int32_t* __restrict__ chunk_len,
                                                                  const float* __restrict__ AB, T* __restrict__ y) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     const int k = blockIdx.y;
     if (c >= width) return;
     const int n = chunk_len[k];
     const int64_t r0 = chunk_start[k];
-    const float zb = z_bias ? z_bias[c] : 0.f, xb = x_bias ? x_bias[c] : 0.f;
-    float S = AB[((int64_t)k * 2) * width + c];
+    float zb[V], xb[V], S[V], o[V];
+    mingru_biases<V>(z_bias, x_bias, c, zb, xb);
+#pragma unroll
+    for (int i = 0; i < V; ++i) S[i] = AB[((int64_t)k * 2) * width + c + i];
+#pragma unroll 8
     for (int t = 0; t < n; ++t) {
-        const MinGruStep<T> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
-        S = st.a * S + st.b;
-        y[(r0 + t) * width + c] = from_f32<T>(S * st.gate);
+        const MinGruStep<T, V> st(zxg + (r0 + t) * 3 * width, width, c, zb, xb);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            S[i] = st.a[i] * S[i] + st.b[i];
+            o[i] = S[i] * st.gate[i];
+        }
+        MinGruVec<T, V>::store(y + (r0 + t) * width + c, o);
     }
 }
 
@@ -278,10 +342,19 @@ PA_API int pa_mingru_scan(const void* d_zxg, const float* d_z_bias, const float*
                           float* d_state, void* d_y, int elem, pa_stream_t stream) {
     PA_CHECK_ARG(d_zxg && width > 0 && d_seq_start && d_seq_len && d_seq_slot && d_state && d_y && num_seqs >= 0);
     if (num_seqs == 0) return PA_OK;
-    dim3 grid((unsigned)((width + 127) / 128), (unsigned)num_seqs);
-    PA_DISPATCH_ELEM(elem, mingru_scan_kernel<T><<<grid, 128, 0, as_stream(stream)>>>(
-                               static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_seq_start, d_seq_len,
-                               d_seq_slot, d_state, static_cast<T*>(d_y)));
+    // two channels per thread where every row, field and state pointer stays aligned for the paired loads
+    const bool pair = width % 2 == 0 && (uintptr_t)d_zxg % 8 == 0 && (uintptr_t)d_y % 8 == 0;
+    if (pair) {
+        dim3 grid((unsigned)((width / 2 + 127) / 128), (unsigned)num_seqs);
+        PA_DISPATCH_ELEM(elem, (mingru_scan_kernel<T, 2><<<grid, 128, 0, as_stream(stream)>>>(
+                                   static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_seq_start, d_seq_len,
+                                   d_seq_slot, d_state, static_cast<T*>(d_y))));
+    } else {
+        dim3 grid((unsigned)((width + 127) / 128), (unsigned)num_seqs);
+        PA_DISPATCH_ELEM(elem, (mingru_scan_kernel<T, 1><<<grid, 128, 0, as_stream(stream)>>>(
+                                   static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_seq_start, d_seq_len,
+                                   d_seq_slot, d_state, static_cast<T*>(d_y))));
+    }
     PA_RETURN_LAUNCH_STATUS();
 }
 
@@ -301,15 +374,21 @@ PA_API int pa_mingru_scan_chunked(const void* d_zxg, const float* d_z_bias, cons
     float* AB = static_cast<float*>(d_workspace);
     const unsigned gx = (unsigned)((width + 127) / 128);
     cudaStream_t st = as_stream(stream);
-    PA_DISPATCH_ELEM(elem, {
-        mingru_chunk_fold_kernel<T><<<dim3(gx, (unsigned)num_chunks), 128, 0, st>>>(
-            static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_chunk_start, d_chunk_len, AB);
-        mingru_chunk_chain_kernel<<<dim3(gx, (unsigned)num_seqs), 128, 0, st>>>(AB, width, d_seq_chunk0, d_seq_nchunks,
-                                                                               d_seq_slot, d_state);
-        mingru_chunk_apply_kernel<T><<<dim3(gx, (unsigned)num_chunks), 128, 0, st>>>(
-            static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_chunk_start, d_chunk_len, AB,
-            static_cast<T*>(d_y));
-    });
+    const bool pair = width % 2 == 0 && (uintptr_t)d_zxg % 8 == 0 && (uintptr_t)d_y % 8 == 0;
+    const unsigned gv = pair ? (unsigned)((width / 2 + 127) / 128) : gx;
+#define PA_MINGRU_CHUNKED(V)                                                                                           \
+    PA_DISPATCH_ELEM(elem, {                                                                                           \
+        mingru_chunk_fold_kernel<T, V><<<dim3(gv, (unsigned)num_chunks), 128, 0, st>>>(                                \
+            static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_chunk_start, d_chunk_len, AB);                  \
+        mingru_chunk_chain_kernel<<<dim3(gx, (unsigned)num_seqs), 128, 0, st>>>(AB, width, d_seq_chunk0, d_seq_nchunks, \
+                                                                               d_seq_slot, d_state);                   \
+        mingru_chunk_apply_kernel<T, V><<<dim3(gv, (unsigned)num_chunks), 128, 0, st>>>(                               \
+            static_cast<const T*>(d_zxg), d_z_bias, d_x_bias, width, d_chunk_start, d_chunk_len, AB,                   \
+            static_cast<T*>(d_y));                                                                                     \
+    })
+    if (pair) PA_MINGRU_CHUNKED(2);
+    else PA_MINGRU_CHUNKED(1);
+#undef PA_MINGRU_CHUNKED
     PA_RETURN_LAUNCH_STATUS();
 }
 

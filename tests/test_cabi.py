@@ -60,6 +60,7 @@ def test_invalid_arguments_rejected_without_device(cabi):
 def test_missing_library_fails_loudly(cabi, monkeypatch):
     monkeypatch.setattr(cabi, "_lib", None)
     monkeypatch.setattr(cabi, "LIB_PATH", "/nonexistent/libpa_b200.so")
+    monkeypatch.setattr(cabi, "CORE_LIB_PATH", "/nonexistent/libpa_b200_core.so")
     with pytest.raises(cabi.PAError):
         cabi.lib()
 

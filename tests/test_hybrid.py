@@ -486,6 +486,75 @@ def test_kernels_alone_against_the_oracle_functions():
     assert (got - want).abs().max() < 1e-4
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,experts,top,width,ff", [(20, 6, 2, 72, 40), (9, 3, 1, 64, 24), (300, 6, 2, 72, 40), (130, 2, 2, 40, 136)])
+def test_grouped_expert_products_in_bfloat16_both_forms(rows, experts, top, width, ff):
+    """pa_moe_gate_up / pa_moe_down on bfloat16 rows: few pairs per expert run the streaming form (weights read straight
+    into the fragments), many the tiled form; both against the double oracle with the same rounding points (the scaled
+    input row, gate, up and their product are bfloat16 values).  One expert gets no pair, one more than a row tile, and
+    the sizes are not multiples of the kernels' tiles."""
+    from llm_decoder import _cabi
+    lib, dev, s = _cabi.lib(), torch.device("cuda"), _cabi.stream
+    g = torch.Generator().manual_seed(rows)
+    bf = torch.bfloat16
+    rnd = lambda t: t.to(bf).double()  # noqa: E731
+    h = torch.randn(rows, width, generator=g).to(bf)
+    wgu = (torch.randn(experts, 2 * ff, width, generator=g) / math.sqrt(width)).to(bf)
+    wdn = (torch.randn(experts, width, ff, generator=g) / math.sqrt(ff)).to(bf)
+    pairs = rows * top
+    # expert 1 is never chosen; expert 0 gets at least half of the pairs
+    ids = torch.randint(0, experts, (pairs,), generator=g)
+    ids[ids == 1] = 0
+    ids[: pairs // 2] = 0
+    ids = ids[torch.randperm(pairs, generator=g)]
+    wts = torch.rand(pairs, generator=g) * 0.9 + 0.1
+    want = torch.zeros(pairs, width, dtype=torch.float64)
+    for i in range(pairs):
+        e = int(ids[i])
+        a = rnd(h[i // top].double() * wts[i].double())
+        gu = wgu[e].double() @ a
+        gt, up = rnd(gu[:ff]), rnd(gu[ff:])
+        want[i] = wdn[e].double() @ rnd(gt * torch.sigmoid(gt) * up)
+    sel_id, sel_w = ids.to(torch.int32).to(dev), wts.to(dev)
+    order = torch.empty(pairs, dtype=torch.int32, device=dev)
+    meta = torch.empty(lib.pa_moe_meta_ints(pairs, experts), dtype=torch.int32, device=dev)
+    _cabi.check(lib.pa_moe_sort(sel_id.data_ptr(), pairs, experts, order.data_ptr(), meta.data_ptr(), s()), "sort")
+    hd, wgud, wdnd = h.to(dev), wgu.to(dev), wdn.to(dev)
+    act = torch.empty(pairs, ff, device=dev, dtype=bf)
+    outp = torch.full((pairs, width), float("nan"), device=dev)
+    _cabi.check(lib.pa_moe_gate_up(hd.data_ptr(), width, wgud.data_ptr(), width, ff, experts, order.data_ptr(), sel_w.data_ptr(),
+                                   top, meta.data_ptr(), pairs, act.data_ptr(), 2, s()), "gate_up")
+    _cabi.check(lib.pa_moe_down(act.data_ptr(), wdnd.data_ptr(), ff, width, experts, order.data_ptr(), meta.data_ptr(), pairs,
+                                outp.data_ptr(), 2, s()), "down")
+    got = outp.double().cpu()
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 2e-2 * want.abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("width,experts,top,elem", [(64, 8, 2, 2), (72, 11, 3, 2), (50, 4, 4, 2), (36, 9, 1, 4), (37, 3, 2, 4)])
+def test_router_scores_and_shared_gate(width, experts, top, elem):
+    """pa_router_topk with the shared-expert gate: widths that allow 16-byte pieces and widths that do not, more experts
+    than one group of the kernel, top == experts."""
+    from llm_decoder import _cabi
+    lib, dev, s = _cabi.lib(), torch.device("cuda"), _cabi.stream
+    g = torch.Generator().manual_seed(width)
+    rows = 45
+    dt = torch.bfloat16 if elem == 2 else torch.float32
+    h = torch.randn(rows, width, generator=g).to(dt)
+    wr, wg = torch.randn(experts, width, generator=g), torch.randn(width, generator=g)
+    sc = torch.sigmoid(h.double() @ wr.double().T)
+    tv, ti = sc.topk(top, -1)
+    hd, wrd, wgd = h.to(dev), wr.to(dev), wg.to(dev)
+    sel_id, sel_w = torch.empty(rows * top, dtype=torch.int32, device=dev), torch.empty(rows * top, device=dev)
+    gate = torch.empty(rows, device=dev)
+    _cabi.check(lib.pa_router_topk(hd.data_ptr(), wrd.data_ptr(), wgd.data_ptr(), rows, width, experts, top, 0, 0,
+                                   sel_id.data_ptr(), sel_w.data_ptr(), gate.data_ptr(), elem, s()), "router")
+    assert torch.equal(sel_id.cpu().view(rows, top).long(), ti)
+    assert (sel_w.cpu().view(rows, top).double() - tv).abs().max() < 1e-5
+    assert (gate.cpu().double() - torch.sigmoid(h.double() @ wg.double())).abs().max() < 1e-5
+
+
 # ---- the tensor-core attention kernel (bfloat16 portions of 16 tokens and more) ---------------------------------------
 def _selector(rows, cols, first):
     m = torch.zeros(rows, cols, dtype=torch.float64)
@@ -495,7 +564,8 @@ def _selector(rows, cols, first):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dim,vdim,heads,kv_heads,tile_size", [(32, 64, 4, 2, 16), (64, 128, 3, 3, 16), (128, 32, 2, 1, 64),
-                                                               (64, 64, 6, 2, 8)])
+                                                               (64, 64, 6, 2, 8), (48, 80, 6, 3, 16), (24, 40, 2, 2, 16),
+                                                               (16, 104, 5, 1, 32), (8, 8, 1, 1, 16)])
 def test_tensor_core_attention_kernel_against_the_oracle(dim, vdim, heads, kv_heads, tile_size):
     """pa_diff_attention, tile kind 2, called directly on bfloat16 rows with a peaked softmax (queries scaled up, so a
     key too many or too few at a tile's, a page's or the causal edge moves a row by O(1)): one sequence fed as 150 + 100
@@ -506,7 +576,8 @@ def test_tensor_core_attention_kernel_against_the_oracle(dim, vdim, heads, kv_he
     from llm_decoder.seq_state import SequenceStateCache
     lib, dev = _cabi.lib(), torch.device("cuda")
     assert lib.pa_diff_attention_mma_tile_tokens(dim, vdim, 2) == 64
-    assert lib.pa_diff_attention_mma_tile_tokens(dim, vdim, 4) == 0 and lib.pa_diff_attention_mma_tile_tokens(24, vdim, 2) == 0
+    assert lib.pa_diff_attention_mma_tile_tokens(dim, vdim, 4) == 0 and lib.pa_diff_attention_mma_tile_tokens(20, vdim, 2) == 0
+    assert lib.pa_diff_attention_mma_tile_tokens(dim, 136, 2) == 0
     qc, kc, vc = heads * 2 * dim, kv_heads * 2 * dim, kv_heads * vdim
     cols = qc + kc + vc
     scale, diff, coef, every, eps = 0.9 / math.sqrt(dim), 0.3, 0.4, 48, 1e-5
