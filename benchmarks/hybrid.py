@@ -221,6 +221,8 @@ def bench_kernels(s, dev):
         o = torch.empty(R, H * V, device=dev, dtype=bf)
         ctas = ntiles * G
         nsplit = 1
+        if single == 1 and ctas >= 148 and lib.pa_diff_attention_mma_head_rows(H, G, D, V, 2):
+            single = 3                                     # the engine's rule: heads as rows on the tensor cores
         if single == 1 and ctas < 4 * 148 and longest > 512:
             nsplit = max(1, min(math.ceil(4 * 148 / ctas), longest // 256, 64))
         wsb = lib.pa_diff_attention_workspace_bytes(ntiles, H, G, V, nsplit)
@@ -291,4 +293,8 @@ def run(sizes=None, kernels=True):
 
 
 if __name__ == "__main__":
-    print(json.dumps(run(), default=float))
+    if len(sys.argv) == 3 and sys.argv[1] == "--kernels":     # the kernels alone at one size (a small case for a profiler)
+        torch.cuda.set_device(0)
+        print(json.dumps({"kernels_" + sys.argv[2]: bench_kernels(SIZES[sys.argv[2]], torch.device("cuda", 0))}, default=float))
+    else:
+        print(json.dumps(run(), default=float))

@@ -593,9 +593,12 @@ int pa_kv_append_rows(void* d_k_pool, void* d_v_pool, const int32_t* d_table, in
  * token (decode): those run on a kernel that streams the keys straight from the pools, 8 warps across each tile's
  * context.  tile_kind 2: bfloat16 only, tiles of up to pa_diff_attention_mma_tile_tokens(dim, vdim, elem) tokens
  * (0 = this shape is not served) on the tensor cores, one query head per CTA, nsplit = 1; PA_ERR_UNSUPPORTED if the
- * shape or an alignment (16-byte q rows and pools) rules it out. */
+ * shape or an alignment (16-byte q rows and pools) rules it out.  tile_kind 3: the same kernel for tiles of ONE token
+ * each, the CTA's rows being the query heads of one key/value head (pa_diff_attention_mma_head_rows != 0: bfloat16,
+ * a served shape, at most 64 heads per key/value head); nsplit = 1, so it wants a batch of many sequences. */
 int pa_diff_attention_tile_tokens(int heads, int kv_heads);
 int pa_diff_attention_mma_tile_tokens(int dim, int vdim, int elem);
+int pa_diff_attention_mma_head_rows(int heads, int kv_heads, int dim, int vdim, int elem);
 size_t pa_diff_attention_workspace_bytes(int num_q_tiles, int heads, int kv_heads, int vdim, int nsplit);
 int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const void* d_k_pool, const void* d_v_pool,
                       const int32_t* d_table, int num_slots, int num_kv_heads, int num_tiles, int total_pages,

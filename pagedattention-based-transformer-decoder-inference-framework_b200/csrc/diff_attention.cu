@@ -40,6 +40,7 @@ struct DiffAttnParams {
     void* out;                  // [rows][heads * vdim]
     int nsplit;
     float* partial;             // nsplit > 1: [(tile, y, split, row)][4 + 2 * vdim]
+    int head_rows;              // tensor-core kernel: every tile is ONE token and the rows are the heads of a kv head
 };
 
 __device__ __forceinline__ void da_geometry(int heads, int kv_heads, int& hpg, int& hc, int& nchunk) {
@@ -291,21 +292,16 @@ __global__ void __launch_bounds__(kDaWarps * 32) diff_attention_merge_kernel(con
 
 // ---- single-token tiles (decode) ------------------------------------------------------------------------------------
 // One CTA = one token x one key/value head x one part of the context; its R >= heads-per-kv-head rows are the query
-// heads of the group.  Every warp is a streaming engine of its own: it takes every kDsWarps-th run of 16 keys of the
-// part and brings the run's key and value rows into ITS ring of `nstage` shared-memory stages with 16-byte cp.async
-// copies (pages located through the table at issue time), nstage - 1 runs ahead of the arithmetic.  Scores: lane
-// (map, key) = (lane / 16, lane % 16) holds the dot products of its key's map half with every row (queries read as
-// broadcasts, key rows padded by 16 bytes: conflict-free); the online softmax of a map runs inside its half-warp.  The
-// weights and the rescale factors pass through shared memory; for the weighted sums the lanes switch to value columns.
-// The warps' (m, l, acc) are merged through shared memory; nsplit > 1 leaves the CTA's partial for
-// diff_attention_merge_kernel.  The query temperature and the scale multiply the float score.
-// Needs key and value rows that are whole 16-byte pieces and R * NV <= 32 (else: the tile kernel).
-constexpr int kDsKeys = 16, kDsWarps = 4, kDsMaxStages = 4;
-
+// heads of the group.  Nothing is staged: each of the 8 warps takes every 8th run of 32 keys, a lane reads ITS key's row
+// with 16-byte loads straight into the two dot products of every row (queries broadcast from shared memory), the warp
+// does the online softmax, then lanes switch to value columns and read each key's value row coalesced.  The 8 warps'
+// (m, l, acc) are merged through shared memory; nsplit > 1 leaves the CTA's partial for diff_attention_merge_kernel.
+// Needs dim a multiple of the 16-byte vector and R * NV <= 32 (the dispatcher falls back to the tile kernel otherwise).
 template <typename T> struct DaVec { static constexpr int N = 16 / sizeof(T); };
 
 template <typename T>
-__device__ __forceinline__ void da_unpack16(const uint4 v, float (&f)[DaVec<T>::N]) {
+__device__ __forceinline__ void da_load16(const T* __restrict__ p, float (&f)[DaVec<T>::N]) {
+    const uint4 v = ldg_stream_128(p);
     if (sizeof(T) == 4) {
         f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
     } else {
@@ -318,189 +314,145 @@ __device__ __forceinline__ void da_unpack16(const uint4 v, float (&f)[DaVec<T>::
     }
 }
 
-// NV consecutive values of a shared-memory row (NV * sizeof(T) is 4, 8, 16 or 32 bytes, the address aligned to it or 16)
+// NV consecutive values of a row starting at element lane * NV (NV * sizeof(T) is 4, 8, 16 or 32 bytes)
 template <typename T, int NV>
-__device__ __forceinline__ void da_lds_packed(const T* __restrict__ p, float (&f)[NV]) {
+__device__ __forceinline__ void da_load_packed(const T* __restrict__ p, float (&f)[NV]) {
     constexpr int BYTES = NV * sizeof(T);
     if (BYTES >= 16) {
 #pragma unroll
         for (int c = 0; c < BYTES / 16; ++c) {
             float t[DaVec<T>::N];
-            da_unpack16<T>(*reinterpret_cast<const uint4*>(p + c * DaVec<T>::N), t);
+            da_load16<T>(p + c * DaVec<T>::N, t);
 #pragma unroll
             for (int i = 0; i < DaVec<T>::N; ++i) f[c * DaVec<T>::N + i] = t[i];
         }
-    } else if (BYTES == 8 && sizeof(T) == 2) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
-        f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
-        f[2 % NV] = __uint_as_float(v.y << 16); f[3 % NV] = __uint_as_float(v.y & 0xffff0000u);
     } else {
 #pragma unroll
         for (int i = 0; i < NV; ++i) f[i] = to_f32<T>(p[i]);
     }
 }
 
-template <int N> __device__ __forceinline__ void cp_async_wait_upto(int pending) {   // pending in [0, N]
-    if (N > 0 && pending >= N) cp_async_wait<N>();
-    else if (N > 0) cp_async_wait_upto<(N > 0 ? N - 1 : 0)>(pending);
-    else cp_async_wait<0>();
-}
-
 template <typename T, int R, int NV, bool PACKED>
-__global__ void __launch_bounds__(kDsWarps * 32) diff_attention_decode_kernel(const DiffAttnParams p, int nstage) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(kDaWarps * 32) diff_attention_decode_kernel(const DiffAttnParams p) {
+    extern __shared__ float smem[];
     constexpr int VN = DaVec<T>::N;
     const int kd = 2 * p.dim;
-    const int krow = kd * (int)sizeof(T) + 16, vrow = p.vdim * (int)sizeof(T);        // bytes per staged key / value row
-    const int stage_bytes = kDsKeys * (krow + vrow);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, key = lane & 15, map = lane >> 4;
-    T* Qs = reinterpret_cast<T*>(smem_raw);                                            // [R][kd]
-    unsigned char* rings = smem_raw + (size_t)R * kd * sizeof(T);
-    unsigned char* ring = rings + (size_t)warp * nstage * stage_bytes;
-    float* Pw = reinterpret_cast<float*>(rings + (size_t)kDsWarps * nstage * stage_bytes) + warp * (kDsKeys * 2 * R + 2 * R);
-    float* Cw = Pw + kDsKeys * 2 * R;                                                  // [2][R] rescale factors
-    float* Ps = reinterpret_cast<float*>(rings + (size_t)kDsWarps * nstage * stage_bytes) + kDsWarps * (kDsKeys * 2 * R + 2 * R);
-    const int pstride = 4 + 2 * p.vdim;                                                // Ps [warps][R][pstride]
+    float* Qs = smem;                                   // [R][kd]
+    float* Ps = Qs + R * kd;                            // [warps][R][4 + 2 * vdim]
+    const int pstride = 4 + 2 * p.vdim;
     const int hpg = p.heads / p.num_kv_heads;
     const int* tile = p.tiles + 4 * blockIdx.x;
     const int row0 = tile[0], slot = tile[2], pos = tile[3];
     const int g = blockIdx.y;
-    const unsigned char* kp = static_cast<const unsigned char*>(p.k_pool);
-    const unsigned char* vp = static_cast<const unsigned char*>(p.v_pool);
-    for (int idx = threadIdx.x; idx < R * kd; idx += blockDim.x) {
-        const int r = idx / kd, d = idx % kd;
-        Qs[idx] = r < hpg ? static_cast<const T*>(p.q)[(int64_t)row0 * p.q_stride + p.q_off + (int64_t)(g * hpg + r) * kd + d]
-                          : from_f32<T>(0.f);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* kp = static_cast<const T*>(p.k_pool);
+    const T* vp = static_cast<const T*>(p.v_pool);
+    {
+        const float temp = 1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f);
+        for (int idx = threadIdx.x; idx < R * kd; idx += blockDim.x) {
+            const int r = idx / kd, d = idx % kd;
+            float v = 0.f;
+            if (r < hpg)
+                v = to_f32<T>(static_cast<const T*>(p.q)[(int64_t)row0 * p.q_stride + p.q_off + (int64_t)(g * hpg + r) * kd + d]) * temp;
+            Qs[idx] = v;
+        }
     }
-    const float sc = p.scale * (1.0f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.0f));
-    float m[R], l[R], a1[R][NV], a2[R][NV];                 // m, l: of this lane's map
+    __syncthreads();
+    float m1[R], l1[R], m2[R], l2[R], a1[R][NV], a2[R][NV];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        m[r] = -INFINITY;
-        l[r] = 0.f;
+        m1[r] = m2[r] = -INFINITY;
+        l1[r] = l2[r] = 0.f;
 #pragma unroll
         for (int i = 0; i < NV; ++i) a1[r][i] = a2[r][i] = 0.f;
     }
     const int total = pos + 1;
-    const int nruns = (total + kDsKeys - 1) / kDsKeys;
-    const int per = (nruns + p.nsplit - 1) / p.nsplit;
-    const int s_begin = blockIdx.z * per, s_end = min(nruns, s_begin + per);
+    const int nsteps = (total + kDaKeys - 1) / kDaKeys;
+    const int per = (nsteps + p.nsplit - 1) / p.nsplit;
+    const int s_begin = blockIdx.z * per, s_end = min(nsteps, s_begin + per);
     const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
-    const int n_my = s_end - s_begin > warp ? (s_end - s_begin - warp + kDsWarps - 1) / kDsWarps : 0;
-    const int ku = (krow - 16) / 16, vu = vrow / 16;         // 16-byte pieces per row
-    auto issue = [&](int i) {                                // this warp's run i -> stage i % nstage
-        const int st = s_begin + warp + i * kDsWarps;
-        const int j = st * kDsKeys + key;
-        int prow = -1;
+    for (int st = s_begin + warp; st < s_end; st += kDaWarps) {
+        const int j = st * kDaKeys + lane;
+        int prow = -1;                                  // pool row of this lane's key
         if (j < total && j / p.tile_size < p.num_tiles) {
             const int page = trow[j / p.tile_size];
             if (page >= 0 && page < p.total_pages) prow = page * p.tile_size + j % p.tile_size;
         }
-        unsigned char* sb = ring + (size_t)(i % nstage) * stage_bytes;
-        if (lane < kDsKeys) *reinterpret_cast<int*>(sb + key * krow + (krow - 16)) = prow >= 0;   // in the row's padding
-        for (int u0 = 0; u0 < kDsKeys * ku; u0 += 32) {
-            const int u = u0 + lane, kk = u < kDsKeys * ku ? u / ku : 0, c = u - kk * ku;
-            const int pr = __shfl_sync(0xffffffffu, prow, kk);
-            if (u < kDsKeys * ku)
-                cp_async_16(smem_u32(sb + kk * krow + c * 16), kp + (pr >= 0 ? (int64_t)pr * (krow - 16) + c * 16 : 0), pr >= 0);
-        }
-        unsigned char* sv = sb + kDsKeys * krow;
-        for (int u0 = 0; u0 < kDsKeys * vu; u0 += 32) {
-            const int u = u0 + lane, kk = u < kDsKeys * vu ? u / vu : 0, c = u - kk * vu;
-            const int pr = __shfl_sync(0xffffffffu, prow, kk);
-            if (u < kDsKeys * vu)
-                cp_async_16(smem_u32(sv + kk * vrow + c * 16), vp + (pr >= 0 ? (int64_t)pr * vrow + c * 16 : 0), pr >= 0);
-        }
-    };
-    for (int i = 0; i < nstage - 1; ++i) {
-        if (i < n_my) issue(i);
-        cp_async_commit();
-    }
-    __syncthreads();                                         // Qs
-    for (int i = 0; i < n_my; ++i) {
-        if (i + nstage - 1 < n_my) issue(i + nstage - 1);
-        cp_async_commit();
-        cp_async_wait_upto<kDsMaxStages - 1>(nstage - 1);    // run i has landed
-        __syncwarp();
-        const unsigned char* sb = ring + (size_t)(i % nstage) * stage_bytes;
-        const T* kr = reinterpret_cast<const T*>(sb + key * krow) + map * p.dim;
-        const bool vis = *reinterpret_cast<const int*>(sb + key * krow + (krow - 16)) != 0;
-        float s[R];
+        float s1[R], s2[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) s[r] = 0.f;
+        for (int r = 0; r < R; ++r) s1[r] = s2[r] = 0.f;
+        if (prow >= 0) {
+            const T* kr = kp + (int64_t)prow * kd;
 #pragma unroll 2
-        for (int d0 = 0; d0 < p.dim; d0 += VN) {
-            float kf[VN];
-            da_unpack16<T>(*reinterpret_cast<const uint4*>(kr + d0), kf);
+            for (int d0 = 0; d0 < p.dim; d0 += VN) {
+                float k1[VN], k2[VN];
+                da_load16<T>(kr + d0, k1);
+                da_load16<T>(kr + p.dim + d0, k2);
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (r >= hpg) continue;
-                float qf[VN];
-                da_unpack16<T>(*reinterpret_cast<const uint4*>(Qs + r * kd + map * p.dim + d0), qf);
+                for (int r = 0; r < R; ++r) {
+                    const float* q1 = Qs + r * kd + d0;
+                    const float* q2 = q1 + p.dim;
 #pragma unroll
-                for (int e = 0; e < VN; ++e) s[r] = fmaf(qf[e], kf[e], s[r]);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float v = vis ? s[r] * sc : -INFINITY;
-            float mx = v;
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float n = fmaxf(m[r], mx);
-            const float c = n == -INFINITY ? 1.f : expf(m[r] - n);
-            const float pe = vis ? expf(v - n) : 0.f;
-            float sum = pe;
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            l[r] = l[r] * c + sum;
-            m[r] = n;
-            Pw[r * 2 * kDsKeys + key * 2 + map] = pe;
-            if (key == 0) Cw[map * R + r] = c;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float c1 = Cw[r], c2 = Cw[R + r];
-#pragma unroll
-            for (int e = 0; e < NV; ++e) {
-                a1[r][e] *= c1;
-                a2[r][e] *= c2;
-            }
-        }
-        const T* vs = reinterpret_cast<const T*>(sb + kDsKeys * krow);
-        const int nk = min(kDsKeys, total - (s_begin + warp + i * kDsWarps) * kDsKeys);
-#pragma unroll 4
-        for (int jj = 0; jj < nk; ++jj) {
-            float v[NV];
-            const T* vr = vs + jj * p.vdim;
-            if (PACKED) {
-                da_lds_packed<T, NV>(vr + lane * NV, v);
-            } else {
-#pragma unroll
-                for (int e = 0; e < NV; ++e) v[e] = lane + 32 * e < p.vdim ? to_f32<T>(vr[lane + 32 * e]) : 0.f;
-            }
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const float2 w12 = *reinterpret_cast<const float2*>(Pw + r * 2 * kDsKeys + jj * 2);   // [row][key][map]
-                const float w1 = w12.x, w2 = w12.y;
-#pragma unroll
-                for (int e = 0; e < NV; ++e) {
-                    a1[r][e] = fmaf(w1, v[e], a1[r][e]);
-                    a2[r][e] = fmaf(w2, v[e], a2[r][e]);
+                    for (int i = 0; i < VN; ++i) {
+                        s1[r] = fmaf(q1[i], k1[i], s1[r]);
+                        s2[r] = fmaf(q2[i], k2[i], s2[r]);
+                    }
                 }
             }
         }
-        __syncwarp();                                        // the stage and Pw / Cw are free again
+        const bool vis = prow >= 0;
+        float p1[R], p2[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float v1 = vis ? s1[r] * p.scale : -INFINITY, v2 = vis ? s2[r] * p.scale : -INFINITY;
+            const float n1 = fmaxf(m1[r], warp_max(v1)), n2 = fmaxf(m2[r], warp_max(v2));
+            const float c1 = n1 == -INFINITY ? 1.f : expf(m1[r] - n1), c2 = n2 == -INFINITY ? 1.f : expf(m2[r] - n2);
+            p1[r] = vis ? expf(v1 - n1) : 0.f;
+            p2[r] = vis ? expf(v2 - n2) : 0.f;
+            l1[r] = l1[r] * c1 + warp_sum(p1[r]);
+            l2[r] = l2[r] * c2 + warp_sum(p2[r]);
+            m1[r] = n1;
+            m2[r] = n2;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                a1[r][i] *= c1;
+                a2[r][i] *= c2;
+            }
+        }
+        const int nk = min(kDaKeys, total - st * kDaKeys);
+#pragma unroll 4
+        for (int jj = 0; jj < nk; ++jj) {
+            const int pr = __shfl_sync(0xffffffffu, prow, jj);
+            float v[NV];
+            if (pr >= 0) {
+                const T* vr = vp + (int64_t)pr * p.vdim;
+                if (PACKED) {
+                    da_load_packed<T, NV>(vr + lane * NV, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < p.vdim ? to_f32<T>(vr[lane + 32 * i]) : 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) v[i] = 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float w1 = __shfl_sync(0xffffffffu, p1[r], jj), w2 = __shfl_sync(0xffffffffu, p2[r], jj);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    a1[r][i] = fmaf(w1, v[i], a1[r][i]);
+                    a2[r][i] = fmaf(w2, v[i], a2[r][i]);
+                }
+            }
+        }
     }
-    cp_async_wait<0>();
     // ---- the warps' partials -> shared memory, merged by warp r for row r
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         float* dst = Ps + ((int64_t)warp * R + r) * pstride;
-        if (key == 0) {
-            dst[2 * map] = m[r];
-            dst[2 * map + 1] = l[r];
+        if (lane == 0) {
+            dst[0] = m1[r]; dst[1] = l1[r]; dst[2] = m2[r]; dst[3] = l2[r];
         }
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -512,17 +464,17 @@ __global__ void __launch_bounds__(kDsWarps * 32) diff_attention_decode_kernel(co
         }
     }
     __syncthreads();
-    for (int r = warp; r < R; r += kDsWarps) {
+    for (int r = warp; r < R; r += kDaWarps) {
         if (r >= hpg) continue;
         float M1 = -INFINITY, M2 = -INFINITY;
-        for (int w = 0; w < kDsWarps; ++w) {
+        for (int w = 0; w < kDaWarps; ++w) {
             M1 = fmaxf(M1, Ps[((int64_t)w * R + r) * pstride + 0]);
             M2 = fmaxf(M2, Ps[((int64_t)w * R + r) * pstride + 2]);
         }
         float L1 = 0.f, L2 = 0.f, b1[NV], b2[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) b1[i] = b2[i] = 0.f;
-        for (int w = 0; w < kDsWarps; ++w) {
+        for (int w = 0; w < kDaWarps; ++w) {
             const float* pw = Ps + ((int64_t)w * R + r) * pstride;
             const float w1 = pw[0] == -INFINITY ? 0.f : expf(pw[0] - M1), w2 = pw[2] == -INFINITY ? 0.f : expf(pw[2] - M2);
             L1 = fmaf(w1, pw[1], L1);
@@ -558,24 +510,14 @@ __global__ void __launch_bounds__(kDsWarps * 32) diff_attention_decode_kernel(co
 
 template <typename T, int R, int NV>
 static int da_decode_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
-    const size_t kd = 2 * (size_t)p.dim;
-    const size_t stage = (size_t)kDsKeys * (kd * sizeof(T) + 16 + (size_t)p.vdim * sizeof(T));
-    const size_t fixed = (size_t)R * kd * sizeof(T) + (size_t)kDsWarps * (kDsKeys * 2 * R + 2 * R) * sizeof(float) +
-                         (size_t)kDsWarps * R * (4 + 2 * p.vdim) * sizeof(float);
-    // the deepest rings (up to kDsMaxStages) that leave room for two CTAs per SM; failing that, for one
-    int nstage = 0;
-    const size_t budgets[2] = {110 * 1024, 220 * 1024};
-    for (int b = 0; b < 2 && nstage < 2; ++b)
-        if (budgets[b] > fixed) nstage = (int)((budgets[b] - fixed) / (kDsWarps * stage));
-    if (nstage < 2) return PA_ERR_UNSUPPORTED;
-    if (nstage > kDsMaxStages) nstage = kDsMaxStages;
-    const size_t smem = fixed + (size_t)nstage * kDsWarps * stage;
+    const size_t smem = ((size_t)R * 2 * p.dim + (size_t)kDaWarps * R * (4 + 2 * p.vdim)) * sizeof(float);
+    if (smem > 200 * 1024) return PA_ERR_UNSUPPORTED;
     const bool packed = p.vdim == 32 * NV && (NV * sizeof(T)) % 4 == 0 && (NV * sizeof(T) <= 16 || (NV * sizeof(T)) % 16 == 0);
     auto kern = packed ? diff_attention_decode_kernel<T, R, NV, true> : diff_attention_decode_kernel<T, R, NV, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)ntiles, (unsigned)p.num_kv_heads, (unsigned)p.nsplit);
-    kern<<<grid, kDsWarps * 32, smem, st>>>(p, nstage);
+    kern<<<grid, kDaWarps * 32, smem, st>>>(p);
     if (p.nsplit > 1) {
         dim3 g2((unsigned)ntiles, (unsigned)p.num_kv_heads);
         diff_attention_merge_kernel<T, NV><<<g2, kDaWarps * 32, 0, st>>>(p);
@@ -587,7 +529,7 @@ static int da_decode_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st
 template <typename T>
 static int da_decode_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
     const int hpg = p.heads / p.num_kv_heads, nv = (p.vdim + 31) / 32;
-    if (p.dim % DaVec<T>::N || p.vdim % DaVec<T>::N || hpg > 8 || nv > 8) return PA_ERR_UNSUPPORTED;
+    if (p.dim % DaVec<T>::N || hpg > 8 || nv > 8) return PA_ERR_UNSUPPORTED;
     if ((uintptr_t)p.k_pool % 16 || (uintptr_t)p.v_pool % 16) return PA_ERR_UNSUPPORTED;
     const int NVc = nv <= 1 ? 1 : nv <= 2 ? 2 : nv <= 4 ? 4 : 8;
     if (hpg <= 4) {
@@ -651,6 +593,9 @@ static int da_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
 // DIM and VDIM are the PADDED sizes (32, 64 or 128): a map's dim values (any multiple of 8 up to DIM) sit at the start
 // of its DIM columns in shared memory and the rest is zero, likewise the value columns; 16-wide steps that are all
 // padding are skipped.
+// head_rows (decoded tokens, many sequences in the batch): a tile is ONE token, the CTA's rows are the query heads that
+// share key/value head blockIdx.y, all at the token's position, so a key/value byte is staged once for the whole group
+// and the dot products of every head with it are one MMA; warps whose 16 rows hold no head only help to copy.
 constexpr int kDmRows = 64, kDmKeys = 64, kDmThreads = 256, kDmPad = 8;
 
 template <int DIM, int VDIM>
@@ -663,14 +608,20 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     __shared__ int key_ok[2][kDmKeys];
 
     const int* tile = p.tiles + 4 * blockIdx.x;
-    const int row0 = tile[0], ntok = tile[1], slot = tile[2], pos0 = tile[3];
-    const int h = blockIdx.y, g = h / (p.heads / p.num_kv_heads);
+    const int row0 = tile[0], slot = tile[2], pos0 = tile[3];
+    const int hpg = p.heads / p.num_kv_heads;
+    const bool hr = p.head_rows != 0;
+    const int ntok = hr ? hpg : tile[1];                     // rows of the CTA that hold a query
+    const int g = hr ? blockIdx.y : blockIdx.y / hpg;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp & 3, map = warp >> 2;
+    const bool active = rg * 16 < ntok;                      // this warp's 16 rows hold at least one query
+    auto q_row = [&](int r) -> int64_t { return hr ? row0 : row0 + r; };             // token row of CTA row r
+    auto q_head = [&](int r) -> int { return hr ? g * hpg + r : (int)blockIdx.y; };   // its query head
     const bf16_t* kp = static_cast<const bf16_t*>(p.k_pool);
     const bf16_t* vp = static_cast<const bf16_t*>(p.v_pool);
     const int32_t* trow = p.table + ((int64_t)slot * p.num_kv_heads + g) * p.num_tiles;
-    const int total = pos0 + ntok;                           // keys any row of the tile may see
+    const int total = pos0 + (hr ? 1 : ntok);                // keys any row of the tile may see
     const int nkt = (total + kDmKeys - 1) / kDmKeys;
     const int dim = p.dim, vdim = p.vdim, kd = 2 * dim;      // the real sizes
 
@@ -678,7 +629,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         const int r = c / (KD / 8), v = c % (KD / 8), mp = v / (DIM / 8), cv = (v % (DIM / 8)) * 8;
         const bool ok = r < ntok && cv < dim;
         const bf16_t* src = static_cast<const bf16_t*>(p.q) +
-                            (ok ? (int64_t)(row0 + r) * p.q_stride + p.q_off + (int64_t)h * kd + mp * dim + cv : 0);
+                            (ok ? q_row(r) * p.q_stride + p.q_off + (int64_t)q_head(r) * kd + mp * dim + cv : 0);
         cp_async_16(smem_u32(Qs + r * KS + v * 8), src, ok);
     }
     auto pool_row = [&](int j) -> int64_t {
@@ -717,7 +668,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     float sc[2];                                             // scale * temperature * log2(e) of the thread's two rows
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        rpos[i] = pos0 + rg * 16 + (lane >> 2) + 8 * i;
+        rpos[i] = pos0 + (hr ? 0 : rg * 16 + (lane >> 2) + 8 * i);
         sc[i] = p.scale * (1.0f + p.temp_coef * logf((float)((rpos[i] + 1) / p.temp_every) + 1.0f)) * 1.4426950408889634f;
     }
 
@@ -727,6 +678,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
+        if (active) {
         float s[8][4];
 #pragma unroll
         for (int t = 0; t < 8; ++t)
@@ -801,6 +753,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
                 mma_bf16_16816(o[2 * np + 1], a, b2, b3);
             }
         }
+        }
         __syncthreads();                                     // this buffer is free for the copies of step kt + 2
     }
     cp_async_wait<0>();
@@ -838,7 +791,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
             const int r = rg * 16 + (lane >> 2) + 8 * i;
             if (r >= ntok) continue;
             const float f = p.out_mult / sqrtf(ss[i] / (float)vdim + p.eps);      // padded columns are exactly zero
-            bf16_t* dst = static_cast<bf16_t*>(p.out) + (int64_t)(row0 + r) * p.heads * vdim + (int64_t)h * vdim + 2 * (lane & 3);
+            bf16_t* dst = static_cast<bf16_t*>(p.out) + q_row(r) * p.heads * vdim + (int64_t)q_head(r) * vdim + 2 * (lane & 3);
 #pragma unroll
             for (int t = 0; t < NT; ++t)
                 if (t * 8 < vdim) *reinterpret_cast<uint32_t*>(dst + t * 8) = pack_bf16x2(o[t][2 * i] * f, o[t][2 * i + 1] * f);
@@ -852,7 +805,7 @@ static int dm_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
     auto kern = diff_attention_mma_kernel<DIM, VDIM>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((unsigned)ntiles, (unsigned)p.heads);
+    dim3 grid((unsigned)ntiles, (unsigned)(p.head_rows ? p.num_kv_heads : p.heads));
     kern<<<grid, kDmThreads, smem, st>>>(p);
     PA_RETURN_LAUNCH_STATUS();
 }
@@ -865,6 +818,7 @@ static int dm_padded(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : 128; }
 // PA_ERR_UNSUPPORTED: this shape or these pointers stay on the float kernel
 static int dm_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
     if (!dm_shape_ok(p.dim, p.vdim) || p.q_stride % 8 || p.q_off % 8) return PA_ERR_UNSUPPORTED;
+    if (p.head_rows && p.heads / p.num_kv_heads > kDmRows) return PA_ERR_UNSUPPORTED;
     if ((uintptr_t)p.q % 16 || (uintptr_t)p.k_pool % 16 || (uintptr_t)p.v_pool % 16 || (uintptr_t)p.out % 4) return PA_ERR_UNSUPPORTED;
     const int dp = dm_padded(p.dim), vp = dm_padded(p.vdim);
 #define PA_DM_CASE(D, V) if (dp == D && vp == V) return dm_launch<D, V>(p, ntiles, st)
@@ -904,6 +858,11 @@ PA_API int pa_diff_attention_mma_tile_tokens(int dim, int vdim, int elem) {
     return elem == 2 && dm_shape_ok(dim, vdim) ? kDmRows : 0;
 }
 
+PA_API int pa_diff_attention_mma_head_rows(int heads, int kv_heads, int dim, int vdim, int elem) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
+    return elem == 2 && dm_shape_ok(dim, vdim) && heads / kv_heads <= kDmRows ? 1 : 0;
+}
+
 PA_API size_t pa_diff_attention_workspace_bytes(int num_tiles_q, int heads, int kv_heads, int vdim, int nsplit) {
     if (nsplit <= 1 || num_tiles_q <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
     const int hpg = heads / kv_heads, hc = hpg < kDaRows ? hpg : kDaRows, nchunk = (hpg + hc - 1) / hc;
@@ -928,10 +887,11 @@ PA_API int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const
     p.num_slots = num_slots; p.num_kv_heads = num_kv_heads; p.num_tiles = num_tiles; p.total_pages = total_pages;
     p.tile_size = tile_size; p.tiles = d_q_tiles; p.heads = heads; p.dim = dim; p.vdim = vdim; p.scale = scale;
     p.temp_coef = temp_coef; p.temp_every = temp_every; p.lambda = lambda; p.out_mult = out_mult; p.eps = eps;
-    p.out = d_out; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace);
+    p.out = d_out; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace); p.head_rows = 0;
     if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
-    if (tile_kind == 2) {       // tiles of up to pa_diff_attention_mma_tile_tokens tokens on the tensor cores
-        if (elem != 2 || nsplit != 1) return PA_ERR_UNSUPPORTED;
+    if (tile_kind == 2 || tile_kind == 3) {   // on the tensor cores: tiles of up to pa_diff_attention_mma_tile_tokens
+        if (elem != 2 || nsplit != 1) return PA_ERR_UNSUPPORTED;   // tokens (2), or one token with its heads as rows (3)
+        p.head_rows = tile_kind == 3;
         return dm_dispatch(p, num_q_tiles, as_stream(stream));
     }
     if (tile_kind == 1) {       // every tile is one token: the streaming kernel, where it serves the shape

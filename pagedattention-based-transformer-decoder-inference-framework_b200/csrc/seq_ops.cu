@@ -220,10 +220,21 @@ __global__ void __launch_bounds__(128) mingru_chunk_chain_kernel(float* __restri
     const int k0 = seq_chunk0[s];
     float* sp = state + (int64_t)seq_slot[s] * width + c;
     float S = *sp;
-    for (int k = k0; k < k0 + n; ++k) {
-        const float A = AB[((int64_t)k * 2) * width + c], B = AB[((int64_t)k * 2 + 1) * width + c];
-        AB[((int64_t)k * 2) * width + c] = S;  // the chunk's incoming state
-        S = A * S + B;
+    // the pairs of 8 chunks are read before any incoming state is written over them: the loads do not wait on the chain
+    constexpr int U = 8;
+    for (int k = k0; k < k0 + n; k += U) {
+        float A[U], B[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const bool ok = k + u < k0 + n;
+            A[u] = ok ? AB[((int64_t)(k + u) * 2) * width + c] : 1.f;
+            B[u] = ok ? AB[((int64_t)(k + u) * 2 + 1) * width + c] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (k + u < k0 + n) AB[((int64_t)(k + u) * 2) * width + c] = S;  // the chunk's incoming state
+            S = A[u] * S + B[u];
+        }
     }
     *sp = S;
 }

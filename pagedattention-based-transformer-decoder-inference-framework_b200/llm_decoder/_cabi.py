@@ -115,6 +115,7 @@ _SIGS = {
     "pa_kv_append_rows": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _vp], _i32),
     "pa_diff_attention_tile_tokens": ([_i32, _i32], _i32),
     "pa_diff_attention_mma_tile_tokens": ([_i32, _i32, _i32], _i32),
+    "pa_diff_attention_mma_head_rows": ([_i32, _i32, _i32, _i32, _i32], _i32),
     "pa_diff_attention_workspace_bytes": ([_i32, _i32, _i32, _i32, _i32], _sz),
     "pa_diff_attention": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
                            _f32, _f32, _i32, _f32, _f32, _f32, _vp, _i32, _i32, _i32, _vp, _sz, _vp], _i32),

@@ -113,6 +113,9 @@ class DiffAttentionMixer:
         self.tile_tokens = model._lib.pa_diff_attention_tile_tokens(self.heads, self.kv_heads)
         # portions of MMA_FROM tokens and more: the tensor-core kernel, where it serves the shape (0 = it does not)
         self.mma_tokens = model._lib.pa_diff_attention_mma_tile_tokens(self.dim, self.vdim, _ELEM[model.act_dtype])
+        # decoded tokens of a batch with at least one (token, kv head) pair per SM: the same kernel, heads as rows
+        self.mma_head_rows = bool(model._lib.pa_diff_attention_mma_head_rows(self.heads, self.kv_heads, self.dim, self.vdim,
+                                                                               _ELEM[model.act_dtype]))
 
     def forward(self, c, hs):
         b, lib, kv, s = c.batch, c.lib, self.kv, _cabi.stream()
@@ -129,7 +132,9 @@ class DiffAttentionMixer:
             # too few CTAs for the chip over a long context: cut the keys (at least 256 per part)
             ctas = ntiles * self.kv_heads * max(1, math.ceil(self.heads // self.kv_heads / 32))
             nsplit = 1
-            if kind != 2 and ctas < 4 * sms and longest > 512:
+            if kind == 1 and self.mma_head_rows and ntiles * self.kv_heads >= sms:
+                kind = 3
+            if kind < 2 and ctas < 4 * sms and longest > 512:
                 nsplit = max(1, min(math.ceil(4 * sms / ctas), longest // 256, 64))
             ws = None
             if nsplit > 1:

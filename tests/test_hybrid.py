@@ -624,6 +624,52 @@ def test_tensor_core_attention_kernel_against_the_oracle(dim, vdim, heads, kv_he
         assert err < 0.04, f"sequence {k}: max abs error {err}"
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,vdim,heads,kv_heads", [(48, 80, 6, 3), (64, 128, 5, 1), (16, 104, 20, 1), (32, 32, 4, 4)])
+def test_decoded_tokens_with_heads_as_rows_equal_the_streaming_kernel(dim, vdim, heads, kv_heads):
+    """pa_diff_attention tile kind 3 (one token per tile, the heads of a key/value head as the rows of a tensor-core
+    tile) against kind 1 (the float streaming kernel, itself held to the oracle elsewhere) on the same pools: sequences
+    at their FIRST token, just inside and just past a 64-key step and a page, and far along; peaked softmax."""
+    from llm_decoder import _cabi
+    from llm_decoder.seq_state import SequenceStateCache
+    lib, dev = _cabi.lib(), torch.device("cuda")
+    assert lib.pa_diff_attention_mma_head_rows(heads, kv_heads, dim, vdim, 2) == 1
+    assert lib.pa_diff_attention_mma_head_rows(heads, kv_heads, dim, vdim, 4) == 0
+    assert lib.pa_diff_attention_mma_head_rows(130, 2, dim, vdim, 2) == 0
+    qc, kc, vc = heads * 2 * dim, kv_heads * 2 * dim, kv_heads * vdim
+    cols = qc + kc + vc
+    lens = [1, 16, 17, 64, 65, 129, 300]
+    g = torch.Generator().manual_seed(dim * heads)
+    states = SequenceStateCache(len(lens), sum(lens) + 16 * len(lens), 16, dev)
+    kv = states.add_kv_layer(kv_heads, 2 * dim, vdim, "bf16")
+    slots = [states.alloc() for _ in lens]
+    # contexts: everything but the last token goes in first (keys and values only), then one token each
+    before = [(sl, [0] * (n - 1)) for sl, n in zip(slots, lens) if n > 1]
+    b0 = states.make_batch(before)
+    ctx = torch.randn(b0.rows, cols, generator=g).to(torch.bfloat16).to(dev)
+    kv.append_rows(ctx, qc, qc + kc, b0.row_slot, b0.row_pos)
+    b1 = states.make_batch([(sl, [0]) for sl in slots])
+    qkv = torch.randn(b1.rows, cols, generator=g)
+    qkv[:, :qc] *= 3.0
+    qkv = qkv.to(torch.bfloat16).to(dev)
+    kv.append_rows(qkv, qc, qc + kc, b1.row_slot, b1.row_pos)
+    tiles, ntiles, _longest = b1.query_tiles(lib.pa_diff_attention_tile_tokens(heads, kv_heads))[1]
+    pt = kv.page_table_
+    outs = {}
+    for kind in (1, 3):
+        out = torch.full((b1.rows, heads * vdim), float("nan"), dtype=torch.bfloat16, device=dev)
+        _cabi.check(lib.pa_diff_attention(qkv.data_ptr(), qkv.stride(0), 0, kv.key_buffer_.data_ptr(), kv.value_buffer_.data_ptr(),
+                                          pt.device_data().data_ptr(), pt.num_beams_, pt.num_heads_, pt.num_tiles_,
+                                          kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, heads, dim, vdim,
+                                          0.9 / math.sqrt(dim), 0.4, 48, 0.45, 0.7, 1e-5, out.data_ptr(), 2, 1, kind, None, 0,
+                                          _cabi.stream()), "pa_diff_attention")
+        torch.cuda.synchronize()
+        outs[kind] = out.double().cpu()
+    assert torch.isfinite(outs[3]).all()
+    err = (outs[3] - outs[1]).abs().max().item()
+    assert err < 0.04, f"max abs difference {err}"
+
+
 def cfg_mma_heads():
     # head sizes the tensor-core attention kernel serves in bfloat16
     return R.make_config([R.attention_layer(heads=4, kv_heads=2, dim=32, vdim=64, coef=0.3, every=16, mlp=R.dense_mlp(64)),
