@@ -613,7 +613,8 @@ int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_w_sh
                    int experts, int top, int score_fn, int renorm, int32_t* d_sel_id, float* d_sel_w,
                    float* d_shared_gate, int elem, pa_stream_t stream);
 /* Group the rows * top (row, choice) pairs by expert: d_order [pairs], d_meta [pa_moe_meta_ints] (offsets and
- * the row tiles of the grouped products). */
+ * the row tiles of the grouped products: pa_moe_tile_rows() pairs each, or 16 where pairs <= 32 * experts, the
+ * regime in which the bfloat16 products stream the weights straight into the MMA fragments). */
 int pa_moe_tile_rows(void);
 int pa_moe_max_tiles(int pairs, int experts);
 size_t pa_moe_meta_ints(int pairs, int experts);

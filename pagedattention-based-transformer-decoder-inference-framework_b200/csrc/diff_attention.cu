@@ -598,14 +598,18 @@ static int da_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
 // and the dot products of every head with it are one MMA; warps whose 16 rows hold no head only help to copy.
 constexpr int kDmRows = 64, kDmKeys = 64, kDmThreads = 256, kDmPad = 8;
 
-template <int DIM, int VDIM>
+// NST key/value buffers form a ring with NST - 1 steps of copies in flight; QR query rows are staged.  Prompt portions:
+// <2, 64> (the arithmetic of a step hides the next step's copies).  Head rows with at most 16 heads per key/value head:
+// <3, 16> -- one 16-row MMA group is all the arithmetic there is, so the copies of two steps must be in flight, and the
+// small query tile leaves room for two such CTAs per SM.
+template <int DIM, int VDIM, int NST, int QR>
 __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const DiffAttnParams p) {
     constexpr int KD = 2 * DIM, KS = KD + kDmPad, VS = VDIM + kDmPad, NT = VDIM / 8;
     extern __shared__ __align__(16) unsigned char dm_smem[];
-    bf16_t* Qs = reinterpret_cast<bf16_t*>(dm_smem);        // [64][KS]
-    bf16_t* Ks = Qs + kDmRows * KS;                          // [2][64][KS]
-    bf16_t* Vs = Ks + 2 * kDmKeys * KS;                      // [2][64][VS]
-    __shared__ int key_ok[2][kDmKeys];
+    bf16_t* Qs = reinterpret_cast<bf16_t*>(dm_smem);        // [QR][KS]
+    bf16_t* Ks = Qs + QR * KS;                               // [NST][64][KS]
+    bf16_t* Vs = Ks + NST * kDmKeys * KS;                    // [NST][64][VS]
+    __shared__ int key_ok[NST][kDmKeys];
 
     const int* tile = p.tiles + 4 * blockIdx.x;
     const int row0 = tile[0], slot = tile[2], pos0 = tile[3];
@@ -615,7 +619,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     const int g = hr ? blockIdx.y : blockIdx.y / hpg;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp & 3, map = warp >> 2;
-    const bool active = rg * 16 < ntok;                      // this warp's 16 rows hold at least one query
+    const bool active = rg * 16 < ntok && rg * 16 < QR;      // this warp's 16 rows hold at least one query
     auto q_row = [&](int r) -> int64_t { return hr ? row0 : row0 + r; };             // token row of CTA row r
     auto q_head = [&](int r) -> int { return hr ? g * hpg + r : (int)blockIdx.y; };   // its query head
     const bf16_t* kp = static_cast<const bf16_t*>(p.k_pool);
@@ -625,7 +629,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     const int nkt = (total + kDmKeys - 1) / kDmKeys;
     const int dim = p.dim, vdim = p.vdim, kd = 2 * dim;      // the real sizes
 
-    for (int c = tid; c < kDmRows * (KD / 8); c += kDmThreads) {
+    for (int c = tid; c < QR * (KD / 8); c += kDmThreads) {
         const int r = c / (KD / 8), v = c % (KD / 8), mp = v / (DIM / 8), cv = (v % (DIM / 8)) * 8;
         const bool ok = r < ntok && cv < dim;
         const bf16_t* src = static_cast<const bf16_t*>(p.q) +
@@ -655,8 +659,11 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
             cp_async_16(smem_u32(Vs + (buf * kDmKeys + key) * VS + v * 8), vp + (ok ? pr * vdim + v * 8 : 0), ok);
         }
     };
-    load_tile(0, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int t = 0; t < NST - 1; ++t) {
+        if (t < nkt) load_tile(t, t);
+        cp_async_commit();
+    }
 
     float o[NT][4];
 #pragma unroll
@@ -673,10 +680,10 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     }
 
     for (int kt = 0; kt < nkt; ++kt) {
-        const int buf = kt & 1, c0 = kt * kDmKeys;
-        if (kt + 1 < nkt) load_tile(kt + 1, buf ^ 1);
+        const int buf = kt % NST, c0 = kt * kDmKeys;
+        if (kt + NST - 1 < nkt) load_tile(kt + NST - 1, (kt + NST - 1) % NST);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<NST - 1>();
         __syncthreads();
         if (active) {
         float s[8][4];
@@ -754,11 +761,11 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
             }
         }
         }
-        __syncthreads();                                     // this buffer is free for the copies of step kt + 2
+        __syncthreads();                                     // this buffer is free for the copies of step kt + NST
     }
     cp_async_wait<0>();
     // ---- a2 through shared memory, then difference, head-wise norm, output factor
-    float* A2 = reinterpret_cast<float*>(Ks);                // [64][VDIM] over the key / value buffers
+    float* A2 = reinterpret_cast<float*>(Ks);                // [QR][VDIM] over the key / value buffers
     float inv[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -766,7 +773,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         inv[i] = 1.0f / l[i];
     }
-    if (map == 1) {
+    if (map == 1 && active) {
 #pragma unroll
         for (int t = 0; t < NT; ++t)
 #pragma unroll
@@ -774,7 +781,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
                 A2[(rg * 16 + (lane >> 2) + 8 * (c >> 1)) * VDIM + t * 8 + 2 * (lane & 3) + (c & 1)] = o[t][c] * inv[c >> 1];
     }
     __syncthreads();
-    if (map == 0) {
+    if (map == 0 && active) {
         float ss[2] = {0.f, 0.f};
 #pragma unroll
         for (int t = 0; t < NT; ++t)
@@ -799,15 +806,21 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     }
 }
 
-template <int DIM, int VDIM>
-static int dm_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
-    const size_t smem = ((size_t)3 * kDmRows * (2 * DIM + kDmPad) + (size_t)2 * kDmKeys * (VDIM + kDmPad)) * sizeof(bf16_t);
-    auto kern = diff_attention_mma_kernel<DIM, VDIM>;
+template <int DIM, int VDIM, int NST, int QR>
+static int dm_launch_as(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    const size_t smem = ((size_t)(QR + NST * kDmKeys) * (2 * DIM + kDmPad) + (size_t)NST * kDmKeys * (VDIM + kDmPad)) * sizeof(bf16_t);
+    auto kern = diff_attention_mma_kernel<DIM, VDIM, NST, QR>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((unsigned)ntiles, (unsigned)(p.head_rows ? p.num_kv_heads : p.heads));
     kern<<<grid, kDmThreads, smem, st>>>(p);
     PA_RETURN_LAUNCH_STATUS();
+}
+
+template <int DIM, int VDIM>
+static int dm_launch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
+    if (p.head_rows && p.heads / p.num_kv_heads <= 16) return dm_launch_as<DIM, VDIM, 3, 16>(p, ntiles, st);
+    return dm_launch_as<DIM, VDIM, 2, kDmRows>(p, ntiles, st);
 }
 
 static bool dm_shape_ok(int dim, int vdim) {

@@ -423,14 +423,18 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
 }
 
 // ---- few rows per expert (decoding): the weights are the traffic -------------------------------------------------------
-// CTA = 4 warps on one row tile (up to 64 sorted pairs of one expert, in groups of 16) x 32 weight rows (MODE 0: 16 gate
-// rows and the matching 16 up rows; MODE 1: 32 output columns).  Nothing is staged: the warps split K into interleaved
-// pieces of 32, and a lane reads 16 bytes (8 consecutive k) of ITS weight row and of its two token rows straight into the
-// mma.sync.m16n8k16 fragments.  The sum over k does not care about order, so the 8 values a lane holds stand for k slots
-// {2t, 2t+1, 2t+8, 2t+9} of two consecutive MMAs -- the same assignment on both operands.  16 weight loads per lane are in
-// flight before the first MMA of a step; many small CTAs keep the whole chip's memory system busy with 16 rows a tile.
-// The warps' partial sums meet in shared memory.  Same argument rules as the kernel above.
-constexpr int kSkChunk = 32, kSkUnroll = 4, kSkWarps = 4, kSkCols = 32, kSkGroups = kGlBM / 16;
+// With few pairs per expert (skinny_ok) the sort cuts the experts' ranges into row tiles of 16.  CTA = 4 warps on one
+// such tile x 32 weight rows (MODE 0: 16 gate rows and the matching 16 up rows; MODE 1: 32 output columns).  Nothing is
+// staged: the warps split K into interleaved pieces of 32, and a lane reads 16 bytes (8 consecutive k) of ITS weight
+// row and of its two token rows straight into the mma.sync.m16n8k16 fragments.  The sum over k does not care about
+// order, so the 8 values a lane holds stand for k slots {2t, 2t+1, 2t+8, 2t+9} of two consecutive MMAs -- the same
+// assignment on both operands.  All loads of a step (16 weight and 8 token pieces per lane) are issued before its first
+// MMA; many small CTAs keep the whole chip's memory system busy.  The warps' partial sums meet in shared memory.
+// Same argument rules as the kernel above.
+constexpr int kSkRows = 16, kSkChunk = 32, kSkUnroll = 4, kSkWarps = 4, kSkCols = 32;
+
+static bool skinny_ok(int pairs, int experts) { return pairs <= 32 * experts; }
+static int moe_tile_rows(int pairs, int experts) { return skinny_ok(pairs, experts) ? kSkRows : kGlBM; }
 
 template <int MODE>
 __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf16_t* __restrict__ A, int64_t lda,
@@ -439,9 +443,7 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
                                                                        const float* __restrict__ a_scale, int top,
                                                                        const int32_t* __restrict__ tiles,
                                                                        bf16_t* __restrict__ out, float* __restrict__ out_f32) {
-    __shared__ float red[kSkWarps][kGlBM][kSkCols + 1];
-    __shared__ int src_row[kGlBM];
-    __shared__ float src_scale[kGlBM];
+    __shared__ float red[kSkWarps][kSkRows][kSkCols + 1];
     const int e = tiles[3 * blockIdx.x];
     if (e < 0) return;
     const int i0 = tiles[3 * blockIdx.x + 1], nr = tiles[3 * blockIdx.x + 2];
@@ -450,23 +452,20 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
     const int w_rows = MODE == 0 ? 2 * n_out : n_out;
     const bf16_t* We = W + (int64_t)e * w_rows * K;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    if (tid < kGlBM) {
-        int sr = -1;
-        float sc = 1.f;
-        if (tid < nr) {
-            const int pair = order[i0 + tid];
-            if (MODE == 0) {
-                sr = pair / top;
-                if (a_scale) sc = a_scale[pair];
-            } else {
-                sr = i0 + tid;
-            }
+    // this lane's two token rows (g and g + 8 of the tile) and their input factors
+    const bf16_t* arow[2];
+    float asc[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i;
+        arow[i] = nullptr;
+        asc[i] = 1.f;
+        if (r < nr) {
+            const int pair = order[i0 + r];
+            arow[i] = A + (int64_t)(MODE == 0 ? pair / top : i0 + r) * lda;
+            if (MODE == 0 && a_scale) asc[i] = a_scale[pair];
         }
-        src_row[tid] = sr;
-        src_scale[tid] = sc;
     }
-    __syncthreads();
-    const int ngroups = (nr + 15) / 16;
     // this lane's weight row of each of the 4 column tiles (nullptr: past the end)
     const bf16_t* wrow[4];
 #pragma unroll
@@ -476,58 +475,42 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
         else { col = n0 + nt * 8 + g; wr = col; }
         wrow[nt] = col < n_out ? We + (int64_t)wr * K : nullptr;
     }
-    float acc[kSkGroups][4][4];
+    float acc[4][4];
 #pragma unroll
-    for (int a = 0; a < kSkGroups; ++a)
+    for (int b = 0; b < 4; ++b)
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+        for (int c = 0; c < 4; ++c) acc[b][c] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int kc = warp * kSkChunk; kc < K; kc += kSkWarps * kSkChunk * kSkUnroll) {
-        uint4 wv[kSkUnroll][4];
+        uint4 wv[kSkUnroll][4], av[kSkUnroll][2];
 #pragma unroll
         for (int u = 0; u < kSkUnroll; ++u) {
             const int k = kc + u * kSkWarps * kSkChunk + 8 * t;
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-                wv[u][nt] = (wrow[nt] && k < K) ? ldg_stream_128(wrow[nt] + k) : zero;
+            for (int nt = 0; nt < 4; ++nt) wv[u][nt] = (wrow[nt] && k < K) ? ldg_stream_128(wrow[nt] + k) : zero;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) av[u][i] = (arow[i] && k < K) ? *reinterpret_cast<const uint4*>(arow[i] + k) : zero;
         }
 #pragma unroll
         for (int u = 0; u < kSkUnroll; ++u) {
-            const int k = kc + u * kSkWarps * kSkChunk + 8 * t;
+            uint4 x = av[u][0], y = av[u][1];
+            if (MODE == 0 && a_scale) {
+                x = scale_bf16x8(x, asc[0]);
+                y = scale_bf16x8(y, asc[1]);
+            }
+            const uint32_t a_lo[4] = {x.x, y.x, x.y, y.y}, a_hi[4] = {x.z, y.z, x.w, y.w};
 #pragma unroll
-            for (int mt = 0; mt < kSkGroups; ++mt) {
-                if (mt >= ngroups) break;
-                const int r0 = mt * 16 + g, r1 = r0 + 8;
-                uint4 x = zero, y = zero;
-                if (src_row[r0] >= 0 && k < K) {
-                    x = *reinterpret_cast<const uint4*>(A + (int64_t)src_row[r0] * lda + k);
-                    if (MODE == 0 && a_scale) x = scale_bf16x8(x, src_scale[r0]);
-                }
-                if (src_row[r1] >= 0 && k < K) {
-                    y = *reinterpret_cast<const uint4*>(A + (int64_t)src_row[r1] * lda + k);
-                    if (MODE == 0 && a_scale) y = scale_bf16x8(y, src_scale[r1]);
-                }
-                const uint32_t a_lo[4] = {x.x, y.x, x.y, y.y}, a_hi[4] = {x.z, y.z, x.w, y.w};
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    mma_bf16_16816(acc[mt][nt], a_lo, wv[u][nt].x, wv[u][nt].y);
-                    mma_bf16_16816(acc[mt][nt], a_hi, wv[u][nt].z, wv[u][nt].w);
-                }
+            for (int nt = 0; nt < 4; ++nt) {
+                mma_bf16_16816(acc[nt], a_lo, wv[u][nt].x, wv[u][nt].y);
+                mma_bf16_16816(acc[nt], a_hi, wv[u][nt].z, wv[u][nt].w);
             }
         }
     }
     // c0,c1 -> row g, columns 2t + {0,1} of the column tile; c2,c3 -> row g + 8
 #pragma unroll
-    for (int mt = 0; mt < kSkGroups; ++mt) {
-        if (mt >= ngroups) break;
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                red[warp][mt * 16 + g + (c >> 1) * 8][nt * 8 + 2 * t + (c & 1)] = acc[mt][nt][c];
-    }
+        for (int c = 0; c < 4; ++c) red[warp][g + (c >> 1) * 8][nt * 8 + 2 * t + (c & 1)] = acc[nt][c];
     __syncthreads();
     for (int idx = tid; idx < nr * NCOL; idx += kSkWarps * 32) {
         const int r = idx / NCOL, c = idx % NCOL;
@@ -547,9 +530,6 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
         }
     }
 }
-
-// few pairs per expert: the streaming form
-static bool skinny_ok(int pairs, int experts) { return pairs <= 32 * experts; }
 
 static bool mma_ok(const void* A, int64_t lda, const void* W, int K) {
     return K % 8 == 0 && lda % 8 == 0 && (uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0;
@@ -583,7 +563,9 @@ PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float*
 PA_API int pa_moe_tile_rows(void) { return kGlBM; }
 
 PA_API int pa_moe_max_tiles(int pairs, int experts) {
-    return pairs <= 0 || experts <= 0 ? 0 : (pairs + kGlBM - 1) / kGlBM + experts;
+    if (pairs <= 0 || experts <= 0) return 0;
+    const int tr = moe_tile_rows(pairs, experts);
+    return (pairs + tr - 1) / tr + experts;
 }
 
 PA_API size_t pa_moe_meta_ints(int pairs, int experts) {
@@ -596,7 +578,7 @@ PA_API int pa_moe_sort(const int32_t* d_sel_id, int pairs, int experts, int32_t*
     if (pairs == 0) return PA_OK;
     if (experts > 4096) return PA_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(3 * experts + 1) * sizeof(int);
-    moe_sort_kernel<<<1, 1024, smem, as_stream(stream)>>>(d_sel_id, pairs, experts, kGlBM, pa_moe_max_tiles(pairs, experts),
+    moe_sort_kernel<<<1, 1024, smem, as_stream(stream)>>>(d_sel_id, pairs, experts, moe_tile_rows(pairs, experts), pa_moe_max_tiles(pairs, experts),
                                                          d_order, d_meta);
     PA_RETURN_LAUNCH_STATUS();
 }
