@@ -597,6 +597,7 @@ static int da_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
 // share key/value head blockIdx.y, all at the token's position, so a key/value byte is staged once for the whole group
 // and the dot products of every head with it are one MMA; warps whose 16 rows hold no head only help to copy.
 constexpr int kDmRows = 64, kDmKeys = 64, kDmThreads = 256, kDmPad = 8;
+static_assert(kDmThreads == 4 * kDmKeys, "four copying threads per key");
 
 // NST key/value buffers form a ring with NST - 1 steps of copies in flight; QR query rows are staged.  Prompt portions:
 // <2, 64> (the arithmetic of a step hides the next step's copies).  Head rows with at most 16 heads per key/value head:
@@ -643,20 +644,27 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         }
         return -1;
     };
+    // four threads per key: ONE page look-up per thread and step; a thread copies every fourth 16-byte piece of its
+    // key's row and of its value row (the four threads of a key cover 64 contiguous bytes per instruction)
     auto load_tile = [&](int kt, int buf) {
-        const int c0 = kt * kDmKeys;
-        for (int c = tid; c < kDmKeys * (KD / 8); c += kDmThreads) {
-            const int key = c / (KD / 8), v = c % (KD / 8), mp = v / (DIM / 8), cv = (v % (DIM / 8)) * 8;
-            const int64_t pr = pool_row(c0 + key);
+        const int key = tid >> 2, q4 = tid & 3;
+        const int64_t pr = pool_row(kt * kDmKeys + key);
+        if (q4 == 0) key_ok[buf][key] = pr >= 0;
+        bf16_t* kdst = Ks + (buf * kDmKeys + key) * KS;
+        const bf16_t* ksrc = kp + (pr >= 0 ? pr * kd : 0);
+#pragma unroll
+        for (int i = 0; i < KD / 32; ++i) {
+            const int v = q4 + 4 * i, mp = v / (DIM / 8), cv = (v % (DIM / 8)) * 8;
             const bool ok = pr >= 0 && cv < dim;
-            cp_async_16(smem_u32(Ks + (buf * kDmKeys + key) * KS + v * 8), kp + (ok ? pr * kd + mp * dim + cv : 0), ok);
-            if (v == 0) key_ok[buf][key] = pr >= 0;
+            cp_async_16(smem_u32(kdst + v * 8), ok ? ksrc + mp * dim + cv : kp, ok);
         }
-        for (int c = tid; c < kDmKeys * (VDIM / 8); c += kDmThreads) {
-            const int key = c / (VDIM / 8), v = c % (VDIM / 8);
-            const int64_t pr = pool_row(c0 + key);
+        bf16_t* vdst = Vs + (buf * kDmKeys + key) * VS;
+        const bf16_t* vsrc = vp + (pr >= 0 ? pr * vdim : 0);
+#pragma unroll
+        for (int i = 0; i < VDIM / 32; ++i) {
+            const int v = q4 + 4 * i;
             const bool ok = pr >= 0 && v * 8 < vdim;
-            cp_async_16(smem_u32(Vs + (buf * kDmKeys + key) * VS + v * 8), vp + (ok ? pr * vdim + v * 8 : 0), ok);
+            cp_async_16(smem_u32(vdst + v * 8), ok ? vsrc + v * 8 : vp, ok);
         }
     };
 #pragma unroll

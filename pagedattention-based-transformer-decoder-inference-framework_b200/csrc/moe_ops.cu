@@ -269,12 +269,13 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
 }
 
 // ---- the same product on the tensor cores (bfloat16 operands, float accumulation) -------------------------------------
-// CTA = 4 warps on a 64-row x 128-weight-row tile, K in steps of 32 through two shared-memory buffers (global loads of
-// step k + 1 are in flight while step k is multiplied).  MODE 0: weight rows [n0, n0 + 64) (gate) and the matching up
+// CTA = 4 warps on a 64-row x 128-weight-row tile, K in steps of 32.  The weight tile comes through a ring of three
+// shared-memory buffers filled by 16-byte cp.async copies two steps ahead; the token rows (gathered, and scaled in MODE
+// 0) go through registers into two buffers, one step ahead.  MODE 0: weight rows [n0, n0 + 64) (gate) and the matching up
 // rows, so a thread holds gate and up of the same output and applies silu(gate) * up itself; MODE 1: 128 output columns.
 // Operands reach the mma.sync.m16n8k16 fragments through ldmatrix from rows padded to 80 bytes (conflict-free).
 // Needs K % 8 == 0 and 16-byte aligned rows (the dispatcher falls back to the kernel above otherwise).
-constexpr int kMmBK = 32, kMmLd = 40, kMmBRows = 128;
+constexpr int kMmBK = 32, kMmLd = 40, kMmBRows = 128, kMmStages = 3;
 
 __device__ __forceinline__ uint4 scale_bf16x8(uint4 v, float sc) {
     __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
                                                           const int32_t* __restrict__ tiles, bf16_t* __restrict__ out,
                                                           float* __restrict__ out_f32) {
     __shared__ __align__(16) bf16_t As[2][kGlBM][kMmLd];
-    __shared__ __align__(16) bf16_t Bs[2][kMmBRows][kMmLd];
+    __shared__ __align__(16) bf16_t Bs[kMmStages][kMmBRows][kMmLd];
     __shared__ int src_row[kGlBM];
     __shared__ float src_scale[kGlBM];
     const int e = tiles[3 * blockIdx.x];
@@ -323,7 +324,7 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
     __syncthreads();
     // loaders: A tile 64 rows x 4 vectors of 8 -> 2 per thread; B tile 128 rows x 4 vectors -> 4 per thread
     const int lv = tid & 3;                                        // vector (8 elements) within the K step
-    uint4 ra[2], rb[4];
+    uint4 ra[2];
     auto load_regs = [&](int k0) {
         const int k = k0 + lv * 8;
 #pragma unroll
@@ -337,6 +338,13 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
             }
             ra[j] = v;
         }
+    };
+    auto store_regs = [&](int buf) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) *reinterpret_cast<uint4*>(&As[buf][(tid >> 2) + j * 32][lv * 8]) = ra[j];
+    };
+    auto copy_weights = [&](int k0, int buf) {                    // 128 weight rows x 4 pieces -> 4 per thread
+        const int k = k0 + lv * 8;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int r = (tid >> 2) + j * 32;                    // tile row 0..127
@@ -344,14 +352,8 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
             if (MODE == 0) wr = r < 64 ? n0 + r : n_out + n0 + (r - 64);
             else wr = n0 + r;
             const bool ok = (MODE == 0 ? (r < 64 ? n0 + r : n0 + r - 64) : n0 + r) < n_out && k < K;
-            rb[j] = ok ? *reinterpret_cast<const uint4*>(We + (int64_t)wr * K + k) : make_uint4(0, 0, 0, 0);
+            cp_async_16(smem_u32(&Bs[buf][r][lv * 8]), ok ? We + (int64_t)wr * K + k : We, ok);
         }
-    };
-    auto store_regs = [&](int buf) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) *reinterpret_cast<uint4*>(&As[buf][(tid >> 2) + j * 32][lv * 8]) = ra[j];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(&Bs[buf][(tid >> 2) + j * 32][lv * 8]) = rb[j];
     };
     const int wm = warp & 1, wn = warp >> 1;                       // 32 rows x (MODE 0: 32 gate + 32 up | MODE 1: 64 columns)
     float acc[2][8][4];
@@ -361,13 +363,21 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
         for (int b = 0; b < 8; ++b)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+    const int nk = (K + kMmBK - 1) / kMmBK;
+#pragma unroll
+    for (int t = 0; t < kMmStages - 1; ++t) {
+        if (t < nk) copy_weights(t * kMmBK, t);
+        cp_async_commit();
+    }
     load_regs(0);
     store_regs(0);
-    __syncthreads();
-    const int nk = (K + kMmBK - 1) / kMmBK;
     for (int kt = 0; kt < nk; ++kt) {
-        const int buf = kt & 1;
+        const int buf = kt & 1, wb = kt % kMmStages;
+        if (kt + kMmStages - 1 < nk) copy_weights((kt + kMmStages - 1) * kMmBK, (kt + kMmStages - 1) % kMmStages);
+        cp_async_commit();
         if (kt + 1 < nk) load_regs((kt + 1) * kMmBK);
+        cp_async_wait<kMmStages - 1>();
+        __syncthreads();                                           // weights of step kt have landed; As[buf] is written
 #pragma unroll
         for (int ks = 0; ks < kMmBK; ks += 16) {
             uint32_t af[2][4];
@@ -380,7 +390,7 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
                 if (MODE == 0) brow = (bp < 2 ? 0 : 64) + wn * 32 + (bp & 1) * 16;
                 else brow = wn * 64 + bp * 16;
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4(smem_u32(&Bs[buf][brow + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
+                ldsm_x4(smem_u32(&Bs[wb][brow + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]), b0, b1, b2, b3);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
                     mma_bf16_16816(acc[a][bp * 2], af[a], b0, b1);

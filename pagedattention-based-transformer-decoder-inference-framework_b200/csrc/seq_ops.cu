@@ -110,6 +110,13 @@ template <> struct MinGruVec<bf16_t, 2> {
     }
 };
 
+// The logistic function of the scan.  float rows: the exact expf and division.  bfloat16 rows: ex2.approx and
+// rcp.approx -- still float arithmetic, relative error ~1e-6, three orders below the rounding of the projections that
+// feed it; the exact forms cost more instructions than the scan has memory time for.
+template <typename T> __device__ __forceinline__ float mingru_sigmoid(float v) {
+    return sizeof(T) == 2 ? __fdividef(1.0f, 1.0f + __expf(-v)) : sigmoid_f32(v);
+}
+
 template <typename T, int V>
 struct MinGruStep {
     float a[V], b[V], gate[V];
@@ -120,12 +127,12 @@ struct MinGruStep {
         MinGruVec<T, V>::load(row + 2 * width + c, gr);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            const float z = sigmoid_f32(zr[i] + zb[i]);
+            const float z = mingru_sigmoid<T>(zr[i] + zb[i]);
             const float u = ur[i] + xb[i];
-            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f32(u);
+            const float cand = u >= 0.f ? u + 0.5f : mingru_sigmoid<T>(u);
             a[i] = 1.0f - z;
             b[i] = z * cand;
-            gate[i] = silu_f32(gr[i]);
+            gate[i] = gr[i] * mingru_sigmoid<T>(gr[i]);
         }
     }
 };
