@@ -620,7 +620,12 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     const int g = hr ? blockIdx.y : blockIdx.y / hpg;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp & 3, map = warp >> 2;
-    const bool active = rg * 16 < ntok && rg * 16 < QR;      // this warp's 16 rows hold at least one query
+    // QR == 16 (head rows, one 16-row group): the four warps of a map SPLIT the 64 keys of a step, 16 each, over the
+    // same rows, and their (m, l, o) meet in shared memory at the end; else a warp owns 16 rows and takes all 64 keys.
+    constexpr bool KSPLIT = QR == 16;
+    constexpr int NKG = KSPLIT ? 1 : 4;                      // groups of 16 keys a warp takes per step
+    const int kg0 = KSPLIT ? rg : 0, rbase = KSPLIT ? 0 : rg * 16;
+    const bool active = KSPLIT || rg * 16 < ntok;            // this warp has rows with a query
     auto q_row = [&](int r) -> int64_t { return hr ? row0 : row0 + r; };             // token row of CTA row r
     auto q_head = [&](int r) -> int { return hr ? g * hpg + r : (int)blockIdx.y; };   // its query head
     const bf16_t* kp = static_cast<const bf16_t*>(p.k_pool);
@@ -683,7 +688,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     float sc[2];                                             // scale * temperature * log2(e) of the thread's two rows
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        rpos[i] = pos0 + (hr ? 0 : rg * 16 + (lane >> 2) + 8 * i);
+        rpos[i] = pos0 + (hr ? 0 : rbase + (lane >> 2) + 8 * i);
         sc[i] = p.scale * (1.0f + p.temp_coef * logf((float)((rpos[i] + 1) / p.temp_every) + 1.0f)) * 1.4426950408889634f;
     }
 
@@ -694,20 +699,20 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         cp_async_wait<NST - 1>();
         __syncthreads();
         if (active) {
-        float s[8][4];
+        float s[2 * NKG][4];
 #pragma unroll
-        for (int t = 0; t < 8; ++t)
+        for (int t = 0; t < 2 * NKG; ++t)
 #pragma unroll
             for (int c = 0; c < 4; ++c) s[t][c] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < DIM; ks += 16) {
             if (ks >= dim) continue;                         // all padding
             uint32_t a[4];
-            ldsm_x4(smem_u32(Qs + (rg * 16 + (lane & 15)) * KS + map * DIM + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+            ldsm_x4(smem_u32(Qs + (rbase + (lane & 15)) * KS + map * DIM + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
 #pragma unroll
-            for (int np = 0; np < 4; ++np) {
+            for (int np = 0; np < NKG; ++np) {
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4(smem_u32(Ks + (buf * kDmKeys + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + map * DIM + ks +
+                ldsm_x4(smem_u32(Ks + (buf * kDmKeys + (kg0 + np) * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + map * DIM + ks +
                                  ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
                 mma_bf16_16816(s[2 * np], a, b0, b1);
                 mma_bf16_16816(s[2 * np + 1], a, b2, b3);
@@ -716,8 +721,8 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         // ---- float scores -> weights (log2 domain)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
-            const int col = t * 8 + 2 * (lane & 3);
+        for (int t = 0; t < 2 * NKG; ++t) {
+            const int col = (2 * kg0 + t) * 8 + 2 * (lane & 3);
             const int2 okk = *reinterpret_cast<const int2*>(&key_ok[buf][col]);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -744,7 +749,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
             }
         }
 #pragma unroll
-        for (int t = 0; t < 8; ++t)
+        for (int t = 0; t < 2 * NKG; ++t)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 s[t][c] = exp2f(s[t][c] - ref[c >> 1]);
@@ -752,7 +757,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
             }
         // ---- weighted sums
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+        for (int kk = 0; kk < NKG; ++kk) {
             uint32_t a[4];
             a[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
             a[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
@@ -762,7 +767,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
             for (int np = 0; np < NT / 2; ++np) {
                 if (np * 16 >= vdim) continue;               // all padding
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(smem_u32(Vs + (buf * kDmKeys + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 +
+                ldsm_x4_trans(smem_u32(Vs + (buf * kDmKeys + (kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + np * 16 +
                                        (lane >> 4) * 8), b0, b1, b2, b3);
                 mma_bf16_16816(o[2 * np], a, b0, b1);
                 mma_bf16_16816(o[2 * np + 1], a, b2, b3);
@@ -773,6 +778,55 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
     }
     cp_async_wait<0>();
     // ---- a2 through shared memory, then difference, head-wise norm, output factor
+    bool fin = active;                                       // this warp finishes rows
+    if (KSPLIT) {
+        // [rg][map][lane][m0 m1 l0 l1 o...] over the key / value buffers (odd stride: conflict-free); warp rg == 0 of
+        // each map merges the four parts into its registers
+        constexpr int PST = 4 + NT * 4 + 1;
+        float* Pm = reinterpret_cast<float*>(Ks);
+        float* mine = Pm + ((rg * 2 + map) * 32 + lane) * PST;
+        mine[0] = m[0]; mine[1] = m[1]; mine[2] = l[0]; mine[3] = l[1];
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mine[4 + t * 4 + c] = o[t][c];
+        __syncthreads();
+        fin = rg == 0;
+        if (fin) {
+            float M[2] = {m[0], m[1]};
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+                const float* pq = Pm + ((q * 2 + map) * 32 + lane) * PST;
+                M[0] = fmaxf(M[0], pq[0]);
+                M[1] = fmaxf(M[1], pq[1]);
+            }
+            float w0[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                w0[i] = m[i] == -INFINITY ? 0.f : exp2f(m[i] - M[i]);
+                l[i] *= w0[i];
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[t][c] *= w0[c >> 1];
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+                const float* pq = Pm + ((q * 2 + map) * 32 + lane) * PST;
+                float wq[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    wq[i] = pq[i] == -INFINITY ? 0.f : exp2f(pq[i] - M[i]);
+                    l[i] = fmaf(wq[i], pq[2 + i], l[i]);
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) o[t][c] = fmaf(wq[c >> 1], pq[4 + t * 4 + c], o[t][c]);
+            }
+        }
+        __syncthreads();                                     // the parts are read: A2 may overwrite them
+    }
     float* A2 = reinterpret_cast<float*>(Ks);                // [QR][VDIM] over the key / value buffers
     float inv[2];
 #pragma unroll
@@ -781,7 +835,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         inv[i] = 1.0f / l[i];
     }
-    if (map == 1 && active) {
+    if (map == 1 && fin) {
 #pragma unroll
         for (int t = 0; t < NT; ++t)
 #pragma unroll
@@ -789,7 +843,7 @@ __global__ void __launch_bounds__(kDmThreads, 2) diff_attention_mma_kernel(const
                 A2[(rg * 16 + (lane >> 2) + 8 * (c >> 1)) * VDIM + t * 8 + 2 * (lane & 3) + (c & 1)] = o[t][c] * inv[c >> 1];
     }
     __syncthreads();
-    if (map == 0 && active) {
+    if (map == 0 && fin) {
         float ss[2] = {0.f, 0.f};
 #pragma unroll
         for (int t = 0; t < NT; ++t)
