@@ -595,7 +595,8 @@ static int da_dispatch(const DiffAttnParams& p, int ntiles, cudaStream_t st) {
 // padding are skipped.
 // head_rows (decoded tokens, many sequences in the batch): a tile is ONE token, the CTA's rows are the query heads that
 // share key/value head blockIdx.y, all at the token's position, so a key/value byte is staged once for the whole group
-// and the dot products of every head with it are one MMA; warps whose 16 rows hold no head only help to copy.
+// and the dot products of every head with it are one MMA.  Up to 16 heads per key/value head: the four warps of a map
+// split the keys of a step; more: warps whose 16 rows hold no head only help to copy.
 constexpr int kDmRows = 64, kDmKeys = 64, kDmThreads = 256, kDmPad = 8;
 static_assert(kDmThreads == 4 * kDmKeys, "four copying threads per key");
 
