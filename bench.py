@@ -279,7 +279,7 @@ def run_ours(args):
     value = world * B / (ms_step * 1e-3)
 
     # ---- end to end: host buffers through AttentionCUDA.forward -------------------------------
-    # host-side I/O buffers live in page-locked memory (the contract's "pinned host memory")
+    # host-side I/O buffers live in page-locked memory (pinned host memory)
     q_host = torch.empty((L, B, H, D)).pin_memory().copy_(q_dev.cpu())
     nk_host = torch.empty((L, B, H, D)).pin_memory().copy_(nk_dev.cpu())
     nv_host = torch.empty((L, B, H, D)).pin_memory().copy_(nv_dev.cpu())

@@ -11,7 +11,7 @@ oracle, frees its memory and returns one dict:  {"us": ..., "achieved": ..., "un
                   large cuBLASLt GEMM (torch._int_mm, 8192^3) reaches on this box in the same run
   c3_group        C3: 32 beam groups x 4 beams, 2048 ctx = 1792 shared + 256 private tokens, achieved on UNIQUE bytes
   c5_splitkv      C5: one sequence of 131072 tokens, pages split over the ranks; three exchange forms
-The oracle is used as the checker only (never timed here).
+The oracle only verifies the results (it is never timed here).
 """
 import os
 import sys

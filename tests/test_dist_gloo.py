@@ -1,5 +1,5 @@
 """Multi-GPU host logic on CPU: world_size-2 gloo process group.  The device kernels
-are replaced by the oracle here only as the CHECKER of the exchange plumbing (partials computed by
+are replaced by the oracle here, only to verify the exchange plumbing (partials computed by
 the oracle over each rank's page range, packed, all-gathered, combined)."""
 import os
 import subprocess
