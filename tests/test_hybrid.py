@@ -409,15 +409,11 @@ def test_trace_runner_and_generate_cli(tmp_path):
     assert ids[:10] == a[:10] and len(ids) == 14
 
 
-@pytest.mark.gpu
-def test_kernels_alone_against_the_oracle_functions():
-    """minGRU scan (plain and chunked), router top-k and the grouped expert products, each called directly."""
-    import llm_decoder as ld
+def _check_scan(lib, dev, s, g, width):
+    """pa_mingru_scan and pa_mingru_scan_chunked on float rows against the recurrence written out in double."""
     from llm_decoder import _cabi
-    lib, dev, s = _cabi.lib(), torch.device("cuda"), _cabi.stream
-    g = torch.Generator().manual_seed(5)
     # --- recurrence: two portions with non-zero incoming state
-    width, lens = 40, [70, 3]
+    lens = [70, 3]
     zxg = torch.randn(sum(lens), 3 * width, generator=g)
     zb, xb = torch.randn(width, generator=g), torch.randn(width, generator=g)
     st0 = torch.randn(4, width, generator=g)
@@ -453,6 +449,17 @@ def test_kernels_alone_against_the_oracle_functions():
         _cabi.check(st, "mingru")
         assert (y.double().cpu() - want_y).abs().max() < 1e-5
         assert (state.double().cpu() - want_s).abs().max() < 1e-5
+
+
+@pytest.mark.gpu
+def test_kernels_alone_against_the_oracle_functions():
+    """minGRU scan (plain and chunked), router top-k and the grouped expert products, each called directly."""
+    import llm_decoder as ld
+    from llm_decoder import _cabi
+    lib, dev, s = _cabi.lib(), torch.device("cuda"), _cabi.stream
+    g = torch.Generator().manual_seed(5)
+    for width in (40, 37):        # paired channels, and the single-channel form of odd widths
+        _check_scan(lib, dev, s, g, width)
     # --- router + grouped experts: 37 rows, 5 experts, top 3, input scaling
     rows, wdt, E, top, ff = 37, 24, 5, 3, 20
     h = torch.randn(rows, wdt, generator=g)
