@@ -543,6 +543,9 @@ int pa_nccl_allgather_combine(void* comm, int world, const float* d_part_m, cons
 /* x[r] = table[ids[r]] (table in the activation type) as float; out-of-range ids give zeros. */
 int pa_embedding_rows(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
                       float* d_out, pa_stream_t stream);
+/* The same rows multiplied by `scale`. */
+int pa_embedding_rows_scaled(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
+                             float scale, float* d_out, pa_stream_t stream);
 /* RMS norm h = x / sqrt(mean(x^2) + eps) * g with g = d_gain_vec[j] (per channel) or the scalar `gain`
  * (d_gain_vec NULL), written to d_out (may be NULL).  With d_shift and d_out_shifted: token shift
  * hs = h + (h' - h) * shift[j], h' = the normalised row d_row_prev[r] of this batch, or, for d_row_prev[r] < 0,
@@ -570,12 +573,22 @@ int pa_mingru_scan_chunked(const void* d_zxg, const float* d_z_bias, const float
 /* x = gelu_erf(x) in place; out[r, j] = silu(gu[r, j]) * gu[r, ff + j]. */
 int pa_gelu_inplace(void* d_x, int64_t n, int elem, pa_stream_t stream);
 int pa_silu_mul(const void* d_gate_up, int64_t rows, int ff, void* d_out, int elem, pa_stream_t stream);
+/* out[r, j] = act(gu[r, j]) * gu[r, ff + j]; act 0 = silu, 1 = relu, 2 = tanh-form gelu. */
+int pa_act_mul(const void* d_gate_up, int64_t rows, int ff, int act, void* d_out, int elem, pa_stream_t stream);
 /* x += mult * (mix + dense + sum_k routed[r * top + k] + shared_gate[r] * shared); every term optional. */
 int pa_residual_combine(float* d_x, int64_t rows, int width, float mult, const void* d_mix, const void* d_dense,
                         const float* d_routed, int top, const void* d_shared, const float* d_shared_gate,
                         int elem, pa_stream_t stream);
 int pa_gather_rows_f32(const float* d_src, const int32_t* d_rows, int n, int width, float* d_dst,
                        pa_stream_t stream);
+/* Norm on a sublayer's OUTPUT: s = y (activation type, optional) + sum_k sel_w[r, k] * routed[r * top + k] (float
+ * rows of the chosen experts, optional; d_sel_w NULL: weights 1); x[r] += s / sqrt(mean(s^2) + eps) * d_gain[j].
+ * d_next (optional): the new x rounded to the activation type, the operand of the next sublayer's products. */
+int pa_residual_add_norm(float* d_x, int64_t rows, int width, float eps, const float* d_gain, const void* d_y,
+                         const float* d_routed, const float* d_sel_w, int top, void* d_next, int elem,
+                         pa_stream_t stream);
+/* out[i] = x[i] in the activation type. */
+int pa_cast_rows(const float* d_x, int64_t n, void* d_out, int elem, pa_stream_t stream);
 
 /* K/V rows of a projection buffer -> page pools with separate key and value widths (K pages
  * [total_pages][tile_size][k_dim], V pages [..][v_dim]); row r goes to position d_row_pos[r] of table row
@@ -607,11 +620,12 @@ int pa_diff_attention(const void* d_q, int64_t q_stride, int q_off, const void* 
                       void* d_out, int elem, int nsplit, int tile_kind, void* d_workspace,
                       size_t workspace_bytes, pa_stream_t stream);
 
-/* Router: float logits h . w_router[e], score_fn 0 = sigmoid / 1 = softmax, the `top` largest (ties: lower id),
- * optionally renormalised; d_w_shared_gate (optional): shared_gate[r] = sigmoid(h . w). */
-int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_w_shared_gate, int rows, int width,
-                   int experts, int top, int score_fn, int renorm, int32_t* d_sel_id, float* d_sel_w,
-                   float* d_shared_gate, int elem, pa_stream_t stream);
+/* Router: float logits h . w_router[e] (+ d_bias[e], optional), score_fn 0 = sigmoid / 1 = softmax over all experts,
+ * the `top` largest (ties: lower id), optionally renormalised; score_fn 2: the `top` largest LOGITS, weights = softmax
+ * over the chosen logits only.  d_w_shared_gate (optional): shared_gate[r] = sigmoid(h . w). */
+int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_bias, const float* d_w_shared_gate,
+                   int rows, int width, int experts, int top, int score_fn, int renorm, int32_t* d_sel_id,
+                   float* d_sel_w, float* d_shared_gate, int elem, pa_stream_t stream);
 /* Group the rows * top (row, choice) pairs by expert: d_order [pairs], d_meta [pa_moe_meta_ints] (offsets and
  * the row tiles of the grouped products: pa_moe_tile_rows() pairs each, or 16 where pairs <= 32 * experts, the
  * regime in which the bfloat16 products stream the weights straight into the MMA fragments). */
@@ -625,9 +639,63 @@ int pa_moe_sort(const int32_t* d_sel_id, int pairs, int experts, int32_t* d_orde
 int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up, int width, int ff, int experts,
                    const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs,
                    void* d_act, int elem, pa_stream_t stream);
+/* pa_moe_gate_up with the gate's activation chosen: 0 = silu, 1 = relu, 2 = relu squared. */
+int pa_moe_gate_up_act(const void* d_h, int64_t ldh, const void* d_w_gate_up, int width, int ff, int experts,
+                       const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs,
+                       int act, void* d_act, int elem, pa_stream_t stream);
+/* Experts without a gate: act[i] = act(W_up[e] a), weights [experts][ff][width]; same a, order and act codes. */
+int pa_moe_up(const void* d_h, int64_t ldh, const void* d_w_up, int width, int ff, int experts,
+              const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs, int act,
+              void* d_act, int elem, pa_stream_t stream);
 /* out_pairs[row * top + choice] = W_down[e] act[i] as float, weights [experts][width][ff]. */
 int pa_moe_down(const void* d_act, const void* d_w_down, int ff, int width, int experts, const int32_t* d_order,
                 const int32_t* d_meta, int pairs, float* d_out_pairs, int elem, pa_stream_t stream);
+
+
+/* ---- attention through a low-rank latent (latent_attention.cu) --------------------------------------------------
+ * The pool keeps ONE row [c (kv_rank) | kr (rot_dim)] per token for all heads (a KVTileCache with one key/value head
+ * and no value pool); keys and values of head h are Wuk_h c and Wuv_h c and are never materialised: the queries are
+ * mapped into the latent (ql_h = Wuk_h^T qp_h, pa_head_linear) and the weighted sums of c are mapped out (Wuv_h).
+ *
+ * pa_rope_table: d_table [rows][dims / 2][cos, sin] of the angles d_row_pos[r] * base^(-2i / dims).
+ * pa_rope_rows: rotates, in place, the interleaved pairs (2i, 2i + 1), i < dims / 2, that start at column
+ *   off + h * head_stride of every row, h < heads.
+ * pa_latent_kv_append: source row r holds [c_raw (kv_rank) | kr_raw (rot_dim)] from column c_off; the pool row at
+ *   position d_row_pos[r] of table row d_row_slot[r] becomes [c_raw / rms(c_raw) * d_gain | kr_raw with its first
+ *   rot_dims entries rotated].
+ * pa_rms_norm_rows: dst[r, :width] = src[r, off : off + width] / rms * d_gain (rows in the activation type).
+ * pa_head_linear: out[r, h, :N] = x[r, h, :K] . W[h] with W [heads][K][N]; x and out addressed by row and head strides.
+ * pa_head_gate: out[r, h * vdim + v] = in[r, h, v] * sigmoid(gate[r * gate_row_stride + h]).
+ * pa_latent_attention: causal softmax attention of `heads` query rows per token, [ql_h | qr_h] . [c_j | kr_j] * scale,
+ *   out[r, h, :kv_rank] = sum_j p_j c_j.  d_q_tiles [num_q_tiles][4] = (first row, tokens, slot, first position): runs of
+ *   at most pa_latent_attention_tile_tokens(heads) consecutive tokens of one portion (tile_kind 0: the float tile
+ *   kernel, any shape, both element types; nsplit > 1 cuts the keys of every tile into that many parts, workspace
+ *   pa_latent_attention_workspace_bytes) or of at most pa_latent_attention_mma_tile_tokens(...) tokens (tile_kind 2:
+ *   bfloat16 on the tensor cores; 0 = this shape is not served; PA_ERR_UNSUPPORTED where a shape or an alignment rules
+ *   it out). */
+int pa_rope_table(const int32_t* d_row_pos, int rows, int dims, float base, float* d_table, pa_stream_t stream);
+int pa_rope_rows(void* d_x, int64_t stride, int off, int head_stride, int heads, int dims, const float* d_table,
+                 int rows, int elem, pa_stream_t stream);
+int pa_latent_kv_append(void* d_pool, const int32_t* d_table, int num_slots, int num_tiles, int total_pages,
+                        int tile_size, int kv_rank, int rot_dim, int rot_dims, const void* d_src, int64_t src_stride,
+                        int c_off, const float* d_gain, float eps, const float* d_rope_table,
+                        const int32_t* d_row_slot, const int32_t* d_row_pos, int rows, int elem, pa_stream_t stream);
+int pa_rms_norm_rows(const void* d_src, int64_t src_stride, int off, int width, float eps, const float* d_gain,
+                     void* d_dst, int64_t dst_stride, int rows, int elem, pa_stream_t stream);
+int pa_head_linear(const void* d_x, int64_t x_row_stride, int64_t x_head_stride, const void* d_W, int heads, int K,
+                   int N, int rows, void* d_out, int64_t o_row_stride, int64_t o_head_stride, int elem,
+                   pa_stream_t stream);
+int pa_head_gate(const void* d_in, int64_t in_row_stride, int64_t in_head_stride, const void* d_gate,
+                 int64_t gate_row_stride, int heads, int vdim, int64_t rows, void* d_out, int elem, pa_stream_t stream);
+int pa_latent_attention_tile_tokens(int heads);
+int pa_latent_attention_mma_tile_tokens(int heads, int kv_rank, int rot_dim, int elem);
+size_t pa_latent_attention_workspace_bytes(int num_q_tiles, int heads, int kv_rank, int nsplit);
+int pa_latent_attention(const void* d_q_lat, int64_t ql_row_stride, int64_t ql_head_stride, const void* d_q_rot,
+                        int64_t qr_row_stride, int64_t qr_head_stride, const void* d_pool, const int32_t* d_table,
+                        int num_slots, int num_tiles, int total_pages, int tile_size, const int32_t* d_q_tiles,
+                        int num_q_tiles, int heads, int kv_rank, int rot_dim, float scale, void* d_out,
+                        int64_t o_row_stride, int64_t o_head_stride, int elem, int nsplit, int tile_kind,
+                        void* d_workspace, size_t workspace_bytes, pa_stream_t stream);
 
 #ifdef __cplusplus
 }

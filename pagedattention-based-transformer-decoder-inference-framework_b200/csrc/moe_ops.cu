@@ -1,12 +1,14 @@
 // moe_ops.cu -- routed feed-forward experts for a batch of token rows.
 //
-//   router_topk_kernel       float router logits, score function (sigmoid or softmax), the `top` largest per row, optional
-//                            renormalisation of the chosen scores, and an optional per-row shared-expert gate
+//   router_topk_kernel       float router logits (+ optional bias), score function (sigmoid, softmax over all experts, or
+//                            softmax over the chosen logits only), the `top` largest per row, optional renormalisation
+//                            of the chosen scores, and an optional per-row shared-expert gate
 //   moe_sort_kernel          groups the (row, choice) pairs by expert (counting sort) and lists the row tiles of the
 //                            grouped matrix products
 //   grouped_linear_kernel    out[i] = f(A[src(i)] * s(i)) . W[expert(i)]^T over the sorted pairs, one CTA per
-//                            (row tile of one expert, column strip); float accumulation; two epilogues: gate/up pair with
-//                            act(gate) * up, or plain rows scattered back to the (row, choice) order as float
+//                            (row tile of one expert, column strip); float accumulation; three epilogues: gate/up pair
+//                            with act(gate) * up, a single up product with act(up), or plain rows scattered back to the
+//                            (row, choice) order as float
 //
 // Weights are [experts][out][in] in the activation type.  Where the design scales the expert's INPUT by the routing
 // weight (instead of its output), `a_scale` carries the weight and the scaled row is rounded to the activation type
@@ -16,7 +18,8 @@
 namespace pa {
 
 // ---- router ---------------------------------------------------------------------------------------------------------
-// One warp per row.  score_fn: 0 = sigmoid, 1 = softmax over the experts.  Ties go to the lower expert id.
+// One warp per row.  score_fn: 0 = sigmoid, 1 = softmax over the experts, 2 = the largest LOGITS are chosen and the
+// weights are the softmax over the chosen logits only.  Ties go to the lower expert id.
 // The dot products run over groups of kRtGroup weight vectors (the experts' rows and, last, the shared-expert gate's):
 // a lane takes 16-byte pieces of the token row and multiplies each into the whole group, so the row is read once per
 // group and the weights with 16-byte loads (VEC; rows whose width or alignment does not allow it go element by element).
@@ -39,6 +42,7 @@ __device__ __forceinline__ void rt_load(const T* p, float (&f)[16 / sizeof(T)]) 
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
+                                                          const float* __restrict__ bias,
                                                           const float* __restrict__ w_shared_gate, int rows, int width,
                                                           int experts, int top, int score_fn, int renorm,
                                                           int32_t* __restrict__ sel_id, float* __restrict__ sel_w,
@@ -91,7 +95,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
             if (e >= nvec) continue;
             const float v = warp_sum(acc[c]);
             if (lane == 0) {
-                if (e < experts) s[e] = v;
+                if (e < experts) s[e] = bias ? v + bias[e] : v;
                 else shared_gate[row] = sigmoid_f32(v);
             }
         }
@@ -100,7 +104,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
     if (lane == 0) {
         if (score_fn == 0) {
             for (int e = 0; e < experts; ++e) s[e] = sigmoid_f32(s[e]);
-        } else {
+        } else if (score_fn == 1) {
             float m = -INFINITY, z = 0.f;
             for (int e = 0; e < experts; ++e) m = fmaxf(m, s[e]);
             for (int e = 0; e < experts; ++e) { s[e] = expf(s[e] - m); z += s[e]; }
@@ -117,7 +121,16 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const T* __restrict__ 
             total += bv;
             s[best] = -INFINITY;
         }
-        if (renorm)
+        if (score_fn == 2) {                          // softmax over the chosen logits (the first chosen is the largest)
+            const float m = sel_w[(int64_t)row * top];
+            total = 0.f;
+            for (int k = 0; k < top; ++k) {
+                const float ex = expf(sel_w[(int64_t)row * top + k] - m);
+                sel_w[(int64_t)row * top + k] = ex;
+                total += ex;
+            }
+        }
+        if (renorm || score_fn == 2)
             for (int k = 0; k < top; ++k) sel_w[(int64_t)row * top + k] /= total;
     }
 }
@@ -171,12 +184,20 @@ constexpr int kGlBM = 64, kGlBN = 64, kGlBK = 32;   // kGlBM is also the row til
 // MODE 0: A rows gathered from the token rows (order[i] / top), scaled by a_scale[order[i]]; W[e] = [2 * n_out][K]
 //         (gate rows, then up rows); out[i][n] = silu(gate) * up in the activation type, sorted order.
 // MODE 1: A rows = sorted rows i; W[e] = [n_out][K]; out_f32[order[i]][n] (scatter to the (row, choice) order).
+// MODE 2: A rows as MODE 0; W[e] = [n_out][K]; out[i][n] = act(product) in the activation type, sorted order.
+// act (MODE 0: of the gate, MODE 2: of the product): 0 = silu, 1 = relu, 2 = relu squared.
+__device__ __forceinline__ float expert_act(float v, int act) {
+    if (act == 1) return fmaxf(v, 0.f);
+    if (act == 2) { const float r = fmaxf(v, 0.f); return r * r; }
+    return silu_f32(v);
+}
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ W,
                                                              int K, int n_out, const int32_t* __restrict__ order,
                                                              const float* __restrict__ a_scale, int top,
                                                              const int32_t* __restrict__ tiles, T* __restrict__ out,
-                                                             float* __restrict__ out_f32) {
+                                                             float* __restrict__ out_f32, int act) {
     __shared__ float As[kGlBK][kGlBM + 1];
     __shared__ float Bs[kGlBK][kGlBN + 1];
     __shared__ float Bu[MODE == 0 ? kGlBK : 1][kGlBN + 1];
@@ -194,7 +215,7 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
         float sc = 1.f;
         if (r < nr) {
             const int pair = order[i0 + r];
-            if (MODE == 0) {
+            if (MODE != 1) {
                 sr = pair / top;
                 if (a_scale) sc = a_scale[pair];
             } else {
@@ -219,7 +240,7 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
             const int sr = src_row[r];
             if (sr >= 0 && k0 + kk < K) {
                 v = to_f32<T>(A[(int64_t)sr * lda + k0 + kk]);
-                if (MODE == 0 && a_scale) v = to_f32<T>(from_f32<T>(v * src_scale[r]));
+                if (MODE != 1 && a_scale) v = to_f32<T>(from_f32<T>(v * src_scale[r]));
             }
             As[kk][r] = v;
         }
@@ -260,7 +281,9 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(const T* __restrict
             if (MODE == 0) {
                 // the two products leave the accumulator in the activation type, like every other projection
                 const float gte = to_f32<T>(from_f32<T>(acc[a][b])), up = to_f32<T>(from_f32<T>(accu[a][b]));
-                out[(int64_t)(i0 + r) * n_out + n] = from_f32<T>(silu_f32(gte) * up);
+                out[(int64_t)(i0 + r) * n_out + n] = from_f32<T>(expert_act(gte, act) * up);
+            } else if (MODE == 2) {
+                out[(int64_t)(i0 + r) * n_out + n] = from_f32<T>(expert_act(to_f32<T>(from_f32<T>(acc[a][b])), act));
             } else {
                 out_f32[(int64_t)order[i0 + r] * n_out + n] = acc[a][b];
             }
@@ -293,7 +316,7 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
                                                           const int32_t* __restrict__ order,
                                                           const float* __restrict__ a_scale, int top,
                                                           const int32_t* __restrict__ tiles, bf16_t* __restrict__ out,
-                                                          float* __restrict__ out_f32) {
+                                                          float* __restrict__ out_f32, int act) {
     __shared__ __align__(16) bf16_t As[2][kGlBM][kMmLd];
     __shared__ __align__(16) bf16_t Bs[kMmStages][kMmBRows][kMmLd];
     __shared__ int src_row[kGlBM];
@@ -311,7 +334,7 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
         float sc = 1.f;
         if (tid < nr) {
             const int pair = order[i0 + tid];
-            if (MODE == 0) {
+            if (MODE != 1) {
                 sr = pair / top;
                 if (a_scale) sc = a_scale[pair];
             } else {
@@ -334,7 +357,7 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
             uint4 v = make_uint4(0, 0, 0, 0);
             if (sr >= 0 && k < K) {
                 v = *reinterpret_cast<const uint4*>(A + (int64_t)sr * lda + k);
-                if (MODE == 0 && a_scale) v = scale_bf16x8(v, src_scale[r]);
+                if (MODE != 1 && a_scale) v = scale_bf16x8(v, src_scale[r]);
             }
             ra[j] = v;
         }
@@ -417,7 +440,17 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(const bf16_t* __restri
                         if (n >= n_out) continue;
                         const float gte = __bfloat162float(__float2bfloat16_rn(acc[a][t][hrow * 2 + c]));
                         const float up = __bfloat162float(__float2bfloat16_rn(acc[a][t + 4][hrow * 2 + c]));
-                        out[(int64_t)(i0 + r) * n_out + n] = __float2bfloat16_rn(silu_f32(gte) * up);
+                        out[(int64_t)(i0 + r) * n_out + n] = __float2bfloat16_rn(expert_act(gte, act) * up);
+                    }
+            } else if (MODE == 2) {
+                bf16_t* dst = out + (int64_t)(i0 + r) * n_out;
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn * 64 + t * 8 + 2 * (lane & 3) + c;
+                        if (n < n_out)
+                            dst[n] = __float2bfloat16_rn(expert_act(__bfloat162float(__float2bfloat16_rn(acc[a][t][hrow * 2 + c])), act));
                     }
             } else {
                 float* dst = out_f32 + (int64_t)order[i0 + r] * n_out;
@@ -452,7 +485,8 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
                                                                        const int32_t* __restrict__ order,
                                                                        const float* __restrict__ a_scale, int top,
                                                                        const int32_t* __restrict__ tiles,
-                                                                       bf16_t* __restrict__ out, float* __restrict__ out_f32) {
+                                                                       bf16_t* __restrict__ out, float* __restrict__ out_f32,
+                                                                       int act) {
     __shared__ float red[kSkWarps][kSkRows][kSkCols + 1];
     const int e = tiles[3 * blockIdx.x];
     if (e < 0) return;
@@ -472,8 +506,8 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
         asc[i] = 1.f;
         if (r < nr) {
             const int pair = order[i0 + r];
-            arow[i] = A + (int64_t)(MODE == 0 ? pair / top : i0 + r) * lda;
-            if (MODE == 0 && a_scale) asc[i] = a_scale[pair];
+            arow[i] = A + (int64_t)(MODE != 1 ? pair / top : i0 + r) * lda;
+            if (MODE != 1 && a_scale) asc[i] = a_scale[pair];
         }
     }
     // this lane's weight row of each of the 4 column tiles (nullptr: past the end)
@@ -504,7 +538,7 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
 #pragma unroll
         for (int u = 0; u < kSkUnroll; ++u) {
             uint4 x = av[u][0], y = av[u][1];
-            if (MODE == 0 && a_scale) {
+            if (MODE != 1 && a_scale) {
                 x = scale_bf16x8(x, asc[0]);
                 y = scale_bf16x8(y, asc[1]);
             }
@@ -531,7 +565,12 @@ __global__ void __launch_bounds__(kSkWarps * 32) grouped_skinny_kernel(const bf1
             for (int w = 0; w < kSkWarps; ++w) { gte += red[w][r][c]; up += red[w][r][16 + c]; }
             gte = __bfloat162float(__float2bfloat16_rn(gte));
             up = __bfloat162float(__float2bfloat16_rn(up));
-            out[(int64_t)(i0 + r) * n_out + n0 + c] = __float2bfloat16_rn(silu_f32(gte) * up);
+            out[(int64_t)(i0 + r) * n_out + n0 + c] = __float2bfloat16_rn(expert_act(gte, act) * up);
+        } else if (MODE == 2) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kSkWarps; ++w) v += red[w][r][c];
+            out[(int64_t)(i0 + r) * n_out + n0 + c] = __float2bfloat16_rn(expert_act(__bfloat162float(__float2bfloat16_rn(v)), act));
         } else {
             float v = 0.f;
 #pragma unroll
@@ -549,11 +588,11 @@ static bool mma_ok(const void* A, int64_t lda, const void* W, int K) {
 
 using namespace pa;
 
-PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_w_shared_gate, int rows, int width,
-                          int experts, int top, int score_fn, int renorm, int32_t* d_sel_id, float* d_sel_w,
-                          float* d_shared_gate, int elem, pa_stream_t stream) {
+PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float* d_bias, const float* d_w_shared_gate,
+                          int rows, int width, int experts, int top, int score_fn, int renorm, int32_t* d_sel_id,
+                          float* d_sel_w, float* d_shared_gate, int elem, pa_stream_t stream) {
     PA_CHECK_ARG(d_h && d_w_router && d_sel_id && d_sel_w && rows >= 0 && width > 0 && experts > 0);
-    PA_CHECK_ARG(top > 0 && top <= experts && (score_fn == 0 || score_fn == 1) && (!d_w_shared_gate || d_shared_gate));
+    PA_CHECK_ARG(top > 0 && top <= experts && score_fn >= 0 && score_fn <= 2 && (!d_w_shared_gate || d_shared_gate));
     if (rows == 0) return PA_OK;
     if (experts > 2048) return PA_ERR_UNSUPPORTED;
     const size_t smem = (size_t)4 * experts * sizeof(float);
@@ -562,7 +601,7 @@ PA_API int pa_router_topk(const void* d_h, const float* d_w_router, const float*
                      (uintptr_t)d_w_shared_gate % 16 == 0;
 #define PA_ROUTER(VEC)                                                                                                 \
     PA_DISPATCH_ELEM(elem, (router_topk_kernel<T, VEC><<<(unsigned)((rows + 3) / 4), 128, smem, as_stream(stream)>>>(  \
-                               static_cast<const T*>(d_h), d_w_router, d_w_shared_gate, rows, width, experts, top,     \
+                               static_cast<const T*>(d_h), d_w_router, d_bias, d_w_shared_gate, rows, width, experts, top, \
                                score_fn, renorm, d_sel_id, d_sel_w, d_shared_gate)))
     if (vec) PA_ROUTER(true);
     else PA_ROUTER(false);
@@ -593,10 +632,11 @@ PA_API int pa_moe_sort(const int32_t* d_sel_id, int pairs, int experts, int32_t*
     PA_RETURN_LAUNCH_STATUS();
 }
 
-PA_API int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up, int width, int ff, int experts,
-                          const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs,
-                          void* d_act, int elem, pa_stream_t stream) {
+PA_API int pa_moe_gate_up_act(const void* d_h, int64_t ldh, const void* d_w_gate_up, int width, int ff, int experts,
+                              const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs,
+                              int act, void* d_act, int elem, pa_stream_t stream) {
     PA_CHECK_ARG(d_h && d_w_gate_up && d_order && d_meta && d_act && width > 0 && ff > 0 && experts > 0 && top > 0);
+    PA_CHECK_ARG(act >= 0 && act <= 2);
     if (pairs <= 0) return PA_OK;
     dim3 grid((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((ff + kGlBN - 1) / kGlBN));
     const int32_t* tiles = d_meta + experts + 1;
@@ -604,18 +644,51 @@ PA_API int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up,
         dim3 gs((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((ff + 15) / 16));
         grouped_skinny_kernel<0><<<gs, kSkWarps * 32, 0, as_stream(stream)>>>(
             static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_gate_up), width, ff, d_order, d_sel_w, top,
-            tiles, static_cast<bf16_t*>(d_act), nullptr);
+            tiles, static_cast<bf16_t*>(d_act), nullptr, act);
         PA_RETURN_LAUNCH_STATUS();
     }
     if (elem == 2 && mma_ok(d_h, ldh, d_w_gate_up, width)) {
         grouped_mma_kernel<0><<<grid, 128, 0, as_stream(stream)>>>(
             static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_gate_up), width, ff, d_order, d_sel_w, top,
-            tiles, static_cast<bf16_t*>(d_act), nullptr);
+            tiles, static_cast<bf16_t*>(d_act), nullptr, act);
         PA_RETURN_LAUNCH_STATUS();
     }
     PA_DISPATCH_ELEM(elem, grouped_linear_kernel<T, 0><<<grid, 256, 0, as_stream(stream)>>>(
                                static_cast<const T*>(d_h), ldh, static_cast<const T*>(d_w_gate_up), width, ff, d_order,
-                               d_sel_w, top, tiles, static_cast<T*>(d_act), nullptr));
+                               d_sel_w, top, tiles, static_cast<T*>(d_act), nullptr, act));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_moe_gate_up(const void* d_h, int64_t ldh, const void* d_w_gate_up, int width, int ff, int experts,
+                          const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs,
+                          void* d_act, int elem, pa_stream_t stream) {
+    return pa_moe_gate_up_act(d_h, ldh, d_w_gate_up, width, ff, experts, d_order, d_sel_w, top, d_meta, pairs, 0, d_act, elem,
+                              stream);
+}
+
+PA_API int pa_moe_up(const void* d_h, int64_t ldh, const void* d_w_up, int width, int ff, int experts,
+                     const int32_t* d_order, const float* d_sel_w, int top, const int32_t* d_meta, int pairs, int act,
+                     void* d_act, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_h && d_w_up && d_order && d_meta && d_act && width > 0 && ff > 0 && experts > 0 && top > 0);
+    PA_CHECK_ARG(act >= 0 && act <= 2);
+    if (pairs <= 0) return PA_OK;
+    const unsigned nt = (unsigned)pa_moe_max_tiles(pairs, experts);
+    const int32_t* tiles = d_meta + experts + 1;
+    if (elem == 2 && mma_ok(d_h, ldh, d_w_up, width) && skinny_ok(pairs, experts)) {
+        grouped_skinny_kernel<2><<<dim3(nt, (unsigned)((ff + kSkCols - 1) / kSkCols)), kSkWarps * 32, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_up), width, ff, d_order, d_sel_w, top, tiles,
+            static_cast<bf16_t*>(d_act), nullptr, act);
+        PA_RETURN_LAUNCH_STATUS();
+    }
+    if (elem == 2 && mma_ok(d_h, ldh, d_w_up, width)) {
+        grouped_mma_kernel<2><<<dim3(nt, (unsigned)((ff + 127) / 128)), 128, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_h), ldh, static_cast<const bf16_t*>(d_w_up), width, ff, d_order, d_sel_w, top, tiles,
+            static_cast<bf16_t*>(d_act), nullptr, act);
+        PA_RETURN_LAUNCH_STATUS();
+    }
+    PA_DISPATCH_ELEM(elem, grouped_linear_kernel<T, 2><<<dim3(nt, (unsigned)((ff + kGlBN - 1) / kGlBN)), 256, 0, as_stream(stream)>>>(
+                               static_cast<const T*>(d_h), ldh, static_cast<const T*>(d_w_up), width, ff, d_order, d_sel_w, top,
+                               tiles, static_cast<T*>(d_act), nullptr, act));
     PA_RETURN_LAUNCH_STATUS();
 }
 
@@ -629,18 +702,18 @@ PA_API int pa_moe_down(const void* d_act, const void* d_w_down, int ff, int widt
         dim3 gs((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + kSkCols - 1) / kSkCols));
         grouped_skinny_kernel<1><<<gs, kSkWarps * 32, 0, as_stream(stream)>>>(
             static_cast<const bf16_t*>(d_act), (int64_t)ff, static_cast<const bf16_t*>(d_w_down), ff, width, d_order, nullptr, 1,
-            tiles, nullptr, d_out_pairs);
+            tiles, nullptr, d_out_pairs, 0);
         PA_RETURN_LAUNCH_STATUS();
     }
     if (elem == 2 && mma_ok(d_act, ff, d_w_down, ff)) {
         dim3 g2((unsigned)pa_moe_max_tiles(pairs, experts), (unsigned)((width + 127) / 128));
         grouped_mma_kernel<1><<<g2, 128, 0, as_stream(stream)>>>(
             static_cast<const bf16_t*>(d_act), (int64_t)ff, static_cast<const bf16_t*>(d_w_down), ff, width, d_order, nullptr, 1,
-            tiles, nullptr, d_out_pairs);
+            tiles, nullptr, d_out_pairs, 0);
         PA_RETURN_LAUNCH_STATUS();
     }
     PA_DISPATCH_ELEM(elem, grouped_linear_kernel<T, 1><<<grid, 256, 0, as_stream(stream)>>>(
                                static_cast<const T*>(d_act), (int64_t)ff, static_cast<const T*>(d_w_down), ff, width,
-                               d_order, nullptr, 1, tiles, nullptr, d_out_pairs));
+                               d_order, nullptr, 1, tiles, nullptr, d_out_pairs, 0));
     PA_RETURN_LAUNCH_STATUS();
 }

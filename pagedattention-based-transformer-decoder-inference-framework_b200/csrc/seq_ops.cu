@@ -11,6 +11,8 @@
 //   mingru_chunk_* kernels    the same recurrence for long portions as a three-pass chunked scan
 //   gelu / silu-mul           activations between two matrix products
 //   residual_combine_kernel   x += m * (mixer + dense ff + sum of routed expert rows + gate * shared expert)
+//   residual_add_norm_kernel  x += rms_norm(y + sum_k w_k * routed expert rows) * gain  (norm on the sublayer's OUTPUT),
+//                             optionally leaving the new x in the activation type for the next sublayer's products
 //
 // Norms, the recurrence with its gates, and the residual sum are computed in float whatever the activation type.
 #include "seq_common.cuh"
@@ -19,12 +21,12 @@ namespace pa {
 
 template <typename T>
 __global__ void embedding_rows_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids, int rows, int width,
-                                      int vocab, float* __restrict__ out) {
+                                      int vocab, float scale, float* __restrict__ out) {
     const int r = blockIdx.x;
     const int id = ids[r];
     const bool ok = id >= 0 && id < vocab;
     const T* src = table + (int64_t)(ok ? id : 0) * width;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) out[(int64_t)r * width + j] = ok ? to_f32<T>(src[j]) : 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) out[(int64_t)r * width + j] = ok ? to_f32<T>(src[j]) * scale : 0.f;
 }
 
 __device__ __forceinline__ float row_inv_rms(const float* __restrict__ xr, int width, float eps, float* sm) {
@@ -280,15 +282,21 @@ __global__ void gelu_kernel(T* __restrict__ x, int64_t n) {
     if (i < n) x[i] = from_f32<T>(gelu_erf_f32(to_f32<T>(x[i])));
 }
 
-// gu rows are [gate (ff) | up (ff)]; out[r, j] = silu(gate_j) * up_j
+// gu rows are [gate (ff) | up (ff)]; out[r, j] = act(gate_j) * up_j, act: 0 = silu, 1 = relu, 2 = tanh-form gelu
+__device__ __forceinline__ float glu_act(float g, int act) {
+    if (act == 1) return fmaxf(g, 0.f);
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return silu_f32(g);
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, int64_t rows, int ff, T* __restrict__ out) {
+__global__ void act_mul_kernel(const T* __restrict__ gu, int64_t rows, int ff, int act, T* __restrict__ out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows * ff) return;
     const int64_t r = i / ff;
     const int j = (int)(i % ff);
     const float g = to_f32<T>(gu[r * 2 * ff + j]), u = to_f32<T>(gu[r * 2 * ff + ff + j]);
-    out[i] = from_f32<T>(silu_f32(g) * u);
+    out[i] = from_f32<T>(glu_act(g, act) * u);
 }
 
 template <typename T>
@@ -312,6 +320,40 @@ __global__ void residual_combine_kernel(float* __restrict__ x, int64_t rows, int
     x[i] = x[i] + mult * s;
 }
 
+// One CTA per row: s = y (activation type, optional) + sum_k w[r, k] * routed[(r, k)] (float pairs, optional);
+// x[r] += s / sqrt(mean(s^2) + eps) * gain; the new row is also left in `next` (activation type) when asked for.
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_norm_kernel(float* __restrict__ x, int width, float eps,
+                                                                const float* __restrict__ gain, const T* __restrict__ y,
+                                                                const float* __restrict__ routed,
+                                                                const float* __restrict__ sel_w, int top,
+                                                                T* __restrict__ next) {
+    extern __shared__ float row[];                    // [width]
+    __shared__ float sm[32];
+    const int64_t r = blockIdx.x;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float s = y ? to_f32<T>(y[r * width + j]) : 0.f;
+        if (routed)
+            for (int k = 0; k < top; ++k) s = fmaf(sel_w ? sel_w[r * top + k] : 1.0f, routed[(r * top + k) * width + j], s);
+        row[j] = s;
+        ss = fmaf(s, s, ss);
+    }
+    ss = block_sum(ss, sm);
+    const float rn = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = x[r * width + j] + row[j] * rn * gain[j];
+        x[r * width + j] = v;
+        if (next) next[r * width + j] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, int64_t n, T* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(x[i]);
+}
+
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ src, const int32_t* __restrict__ rows, int n, int width,
                                    T* __restrict__ dst) {
@@ -324,13 +366,18 @@ __global__ void gather_rows_kernel(const T* __restrict__ src, const int32_t* __r
 
 using namespace pa;
 
-PA_API int pa_embedding_rows(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
-                             float* d_out, pa_stream_t stream) {
+PA_API int pa_embedding_rows_scaled(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
+                                    float scale, float* d_out, pa_stream_t stream) {
     PA_CHECK_ARG(d_table && d_ids && d_out && rows >= 0 && width > 0 && vocab > 0);
     if (rows == 0) return PA_OK;
     PA_DISPATCH_ELEM(elem, embedding_rows_kernel<T><<<rows, 256, 0, as_stream(stream)>>>(
-                               static_cast<const T*>(d_table), d_ids, rows, width, vocab, d_out));
+                               static_cast<const T*>(d_table), d_ids, rows, width, vocab, scale, d_out));
     PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_embedding_rows(const void* d_table, int elem, const int32_t* d_ids, int rows, int width, int vocab,
+                             float* d_out, pa_stream_t stream) {
+    return pa_embedding_rows_scaled(d_table, elem, d_ids, rows, width, vocab, 1.0f, d_out, stream);
 }
 
 PA_API int pa_rms_norm_shift(const float* d_x, int rows, int width, float eps, float gain, const float* d_gain_vec,
@@ -417,12 +464,37 @@ PA_API int pa_gelu_inplace(void* d_x, int64_t n, int elem, pa_stream_t stream) {
     PA_RETURN_LAUNCH_STATUS();
 }
 
-PA_API int pa_silu_mul(const void* d_gate_up, int64_t rows, int ff, void* d_out, int elem, pa_stream_t stream) {
-    PA_CHECK_ARG(d_gate_up && d_out && rows >= 0 && ff > 0);
+PA_API int pa_act_mul(const void* d_gate_up, int64_t rows, int ff, int act, void* d_out, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_gate_up && d_out && rows >= 0 && ff > 0 && act >= 0 && act <= 2);
     if (rows == 0) return PA_OK;
     const int64_t n = rows * ff;
-    PA_DISPATCH_ELEM(elem, silu_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
-                               static_cast<const T*>(d_gate_up), rows, ff, static_cast<T*>(d_out)));
+    PA_DISPATCH_ELEM(elem, act_mul_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               static_cast<const T*>(d_gate_up), rows, ff, act, static_cast<T*>(d_out)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_silu_mul(const void* d_gate_up, int64_t rows, int ff, void* d_out, int elem, pa_stream_t stream) {
+    return pa_act_mul(d_gate_up, rows, ff, 0, d_out, elem, stream);
+}
+
+PA_API int pa_residual_add_norm(float* d_x, int64_t rows, int width, float eps, const float* d_gain, const void* d_y,
+                                const float* d_routed, const float* d_sel_w, int top, void* d_next, int elem,
+                                pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && d_gain && rows >= 0 && width > 0 && (d_y || d_routed) && (!d_routed || top > 0));
+    if (rows == 0) return PA_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) return PA_ERR_UNSUPPORTED;
+    PA_DISPATCH_ELEM(elem, residual_add_norm_kernel<T><<<(unsigned)rows, 256, smem, as_stream(stream)>>>(
+                               d_x, width, eps, d_gain, static_cast<const T*>(d_y), d_routed, d_sel_w, top,
+                               static_cast<T*>(d_next)));
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+PA_API int pa_cast_rows(const float* d_x, int64_t n, void* d_out, int elem, pa_stream_t stream) {
+    PA_CHECK_ARG(d_x && d_out && n >= 0);
+    if (n == 0) return PA_OK;
+    PA_DISPATCH_ELEM(elem, cast_rows_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+                               d_x, n, static_cast<T*>(d_out)));
     PA_RETURN_LAUNCH_STATUS();
 }
 

@@ -119,13 +119,32 @@ _SIGS = {
     "pa_diff_attention_workspace_bytes": ([_i32, _i32, _i32, _i32, _i32], _sz),
     "pa_diff_attention": ([_vp, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
                            _f32, _f32, _i32, _f32, _f32, _f32, _vp, _i32, _i32, _i32, _vp, _sz, _vp], _i32),
-    "pa_router_topk": ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp], _i32),
+    "pa_router_topk": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i32, _vp], _i32),
     "pa_moe_tile_rows": ([], _i32),
     "pa_moe_max_tiles": ([_i32, _i32], _i32),
     "pa_moe_meta_ints": ([_i32, _i32], _sz),
     "pa_moe_sort": ([_vp, _i32, _i32, _vp, _vp, _vp], _i32),
     "pa_moe_gate_up": ([_vp, _i64, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _i32, _vp], _i32),
     "pa_moe_down": ([_vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _vp], _i32),
+    "pa_moe_gate_up_act": ([_vp, _i64, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _vp, _i32, _vp], _i32),
+    "pa_moe_up": ([_vp, _i64, _vp, _i32, _i32, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _vp, _i32, _vp], _i32),
+    "pa_embedding_rows_scaled": ([_vp, _i32, _vp, _i32, _i32, _i32, _f32, _vp, _vp], _i32),
+    "pa_act_mul": ([_vp, _i64, _i32, _i32, _vp, _i32, _vp], _i32),
+    "pa_residual_add_norm": ([_vp, _i64, _i32, _f32, _vp, _vp, _vp, _vp, _i32, _vp, _i32, _vp], _i32),
+    "pa_cast_rows": ([_vp, _i64, _vp, _i32, _vp], _i32),
+    # attention through a low-rank latent (latent_attention.cu)
+    "pa_rope_table": ([_vp, _i32, _i32, _f32, _vp, _vp], _i32),
+    "pa_rope_rows": ([_vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _vp], _i32),
+    "pa_latent_kv_append": ([_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _vp, _f32, _vp, _vp, _vp,
+                             _i32, _i32, _vp], _i32),
+    "pa_rms_norm_rows": ([_vp, _i64, _i32, _i32, _f32, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
+    "pa_head_linear": ([_vp, _i64, _i64, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _i64, _i32, _vp], _i32),
+    "pa_head_gate": ([_vp, _i64, _i64, _vp, _i64, _i32, _i32, _i64, _vp, _i32, _vp], _i32),
+    "pa_latent_attention_tile_tokens": ([_i32], _i32),
+    "pa_latent_attention_mma_tile_tokens": ([_i32, _i32, _i32, _i32], _i32),
+    "pa_latent_attention_workspace_bytes": ([_i32, _i32, _i32, _i32], _sz),
+    "pa_latent_attention": ([_vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32, _i32,
+                             _f32, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _sz, _vp], _i32),
 }
 
 EXPORTS = tuple(_SIGS)

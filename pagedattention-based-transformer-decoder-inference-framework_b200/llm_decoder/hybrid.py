@@ -1,6 +1,9 @@
 """HybridDecoder -- a config-driven decoder stack over a ragged batch: every layer is one MIXER (picked by the layer's
-`type` from MIXERS) plus an optional FEED-FORWARD (picked by `mlp.kind` from FEED_FORWARDS) that both read the same
-pre-norm output; the residual stream is float.  The `Megusun` design is served by this class:
+`type` from MIXERS) plus an optional FEED-FORWARD (picked by `mlp.kind` from FEED_FORWARDS); the residual stream is
+float.  A DESIGN (config "architecture", table DESIGNS) fixes how a layer is wired and with which constants the
+mechanisms are built.  Two designs are served.
+
+`Megusun` (wiring 'parallel': mixer and feed-forward both read the same pre-norm output):
 
     x      = embed[token]                                         (float residual)
     h      = x / sqrt(mean(x^2) + eps) * g_l                      (one number g_l per layer)
@@ -15,6 +18,22 @@ pre-norm output; the residual stream is float.  The `Megusun` design is served b
   ff 'dense'         W_down gelu_erf(W_up h)
   ff 'moe'           sigmoid router, top-k by score, the score scales the expert's INPUT, experts W_down(silu(W_gate a) *
                      W_up a), plus a shared expert gated by sigmoid(w_sg . h)
+
+`Domilix` (wiring 'post_norm': the sublayers read x itself, one after the other, and the norm is on their OUTPUT):
+
+    x      = embed[token] * s_embed
+    x     += N(mixer_l(x); w1_l),  then  x += N(ff_l(x); w2_l)         N(y; w) = y / sqrt(mean(y^2) + eps) * w  (per channel)
+    logits = head . N(x; w_final)
+
+  mixer 'latent_attention'   queries through a normed latent (q = W_uq N(W_dq x)), ONE cached row per token
+                     [c = N(first kv_rank rows of W_dkv x) | kr = rotated last rot_dim rows] shared by all heads; keys and
+                     values of head h are W_uk_h c and W_uv_h c, applied to the QUERY (ql_h = W_uk_h^T q_h) and to the
+                     weighted sum of c instead of to the cache (csrc/latent_attention.cu); interleaved-pair rotation of
+                     the rot_dim part of q and k; causal softmax; per-head output gate sigmoid(W_g x)_h; a layer with
+                     `kv_from: j` has no W_dkv and reads layer j's pool
+  ff 'dense'         W_down (relu(W_gate h) * (W_up h))
+  ff 'moe'           logits W_r h + b, the `top` largest, weights = softmax over the chosen logits, applied to the
+                     expert's OUTPUT; experts W_down relu(W_up h)^2
 
 Every size and constant comes from config.json (or a tensor's shape); the constants a design fixes are the arguments
 the mechanisms are constructed with.  Two precisions: 'bfloat16' (matrix products and their activations in bfloat16
@@ -52,8 +71,22 @@ class _Ctx:
         self.dt, self.elem, self.dev = model.act_dtype, _ELEM[model.act_dtype], model.device
         self.R = batch.rows
 
+        self._rope = {}
+
     def empty(self, *shape, dtype=None):
         return torch.empty(shape, dtype=dtype or self.dt, device=self.dev)
+
+    def rope_table(self, dims, base):
+        """[rows][dims / 2][cos, sin] of this step's rows (float), computed once per step and rotation."""
+        key = (dims, base)
+        if key not in self._rope:
+            t = None
+            if dims > 0:
+                t = self.empty(self.R, dims // 2, 2, dtype=torch.float32)
+                _chk(self.lib.pa_rope_table(self.batch.row_pos.data_ptr(), self.R, dims, base, t.data_ptr(), _cabi.stream()),
+                     "pa_rope_table")
+            self._rope[key] = t
+        return self._rope[key]
 
 
 # ---------------------------------------------------------------------------------------------------------------- mixers
@@ -149,35 +182,165 @@ class DiffAttentionMixer:
         return c.model._linear(out, self.w_o)
 
 
-MIXERS = {"mingru": MinGRUMixer, "attention": DiffAttentionMixer}
+class LatentAttentionMixer:
+    """Attention through a low-rank latent over a paged pool with ONE row per token (KVTileCache with one key/value head
+    and no value pool: row = [c | kr]).  The per-head key and value maps are applied on the query side and after the
+    weighted sum (pa_head_linear), so a step reads kv_rank + rot_dim values per cached token whatever the head count."""
+    kind = "latent_attention"
+
+    def __init__(self, model, prefix, cfg, W):
+        H, self.dim, self.rot_dim, self.vdim = int(cfg["heads"]), int(cfg["dim"]), int(cfg["rot_dim"]), int(cfg["vdim"])
+        self.heads, self.kv_rank, self.q_rank = H, int(cfg["kv_rank"]), int(cfg["q_rank"])
+        rot = cfg.get("rot") or {}
+        self.rot_dims, self.rot_base = int(rot.get("dims", self.rot_dim)), float(rot.get("base", 10000.0))
+        if self.rot_dims > self.rot_dim or self.rot_dims % 2:
+            raise ValueError("rot.dims must be even and at most rot_dim")
+        self.scale = float(cfg["scale"])
+        self.kv_from = cfg.get("kv_from")
+        self.own_kv = self.kv_from is None
+        qd, kd = self.dim + self.rot_dim, self.kv_rank + self.rot_dim
+        self.qd, self.kd = qd, kd
+        for name, shape in (("dq", (self.q_rank, model.width)), ("uq", (H * qd, self.q_rank)), ("uk", (H * self.dim, self.kv_rank)),
+                            ("uv", (H * self.vdim, self.kv_rank)), ("g", (H, model.width)), ("o", (model.width, H * self.vdim))):
+            if tuple(W[prefix + name].shape) != shape:
+                raise ValueError(f"{prefix}{name}: shape {tuple(W[prefix + name].shape)} does not match the config {shape}")
+        # one product for everything that reads the layer's input: [dq | dkv (own pool only) | g]
+        parts = [W[prefix + "dq"]] + ([W[prefix + "dkv"]] if self.own_kv else []) + [W[prefix + "g"]]
+        self.w_in = model._weight(torch.cat(parts, 0))
+        self.c_off = self.q_rank
+        self.g_off = self.q_rank + (kd if self.own_kv else 0)
+        self.dq_gain = model._f32(W[prefix + "dq.norm"])
+        self.w_uq = model._weight(W[prefix + "uq"])
+        self.w_uk = model._weight_raw(W[prefix + "uk"].reshape(H, self.dim, self.kv_rank))                    # [H][dim][kv_rank]
+        self.w_uv = model._weight_raw(W[prefix + "uv"].reshape(H, self.vdim, self.kv_rank).transpose(1, 2))   # [H][kv_rank][vdim]
+        self.w_o = model._weight(W[prefix + "o"])
+        if self.own_kv:
+            if tuple(W[prefix + "dkv"].shape) != (kd, model.width):
+                raise ValueError(f"{prefix}dkv: shape does not match kv_rank + rot_dim")
+            self.dkv_gain = model._f32(W[prefix + "dkv.norm"])
+            self.kv = model.states.add_kv_layer(1, kd, 0, _KV[model.act_dtype])
+        else:
+            j = int(self.kv_from)
+            src = model.layers[j].mixer if 0 <= j < len(model.layers) else None
+            if not isinstance(src, LatentAttentionMixer) or not src.own_kv:
+                raise ValueError(f"{prefix}: kv_from must name an earlier latent-attention layer with a pool of its own")
+            if (src.kv_rank, src.rot_dim, src.rot_dims, src.rot_base) != (self.kv_rank, self.rot_dim, self.rot_dims, self.rot_base):
+                raise ValueError(f"{prefix}: kv_rank, rot_dim and rotation must equal those of layer {j}")
+            self.kv = src.kv
+        self.tile_tokens = model._lib.pa_latent_attention_tile_tokens(H)
+        self.mma_tokens = model._lib.pa_latent_attention_mma_tile_tokens(H, self.kv_rank, self.rot_dim, _ELEM[model.act_dtype])
+
+    def _head_linear(self, c, x, x_rs, x_hs, w, K, N, out, x_off=0):
+        H = self.heads
+        _chk(c.lib.pa_head_linear(x.data_ptr() + x_off * c.elem, x_rs, x_hs, w.data_ptr(), H, K, N, c.R, out.data_ptr(),
+                                  H * N, N, c.elem, _cabi.stream()), "pa_head_linear")
+
+    def forward(self, c, h):
+        b, lib, kv, s, R, H = c.batch, c.lib, self.kv, _cabi.stream(), c.R, self.heads
+        proj = c.model._linear(h, self.w_in)
+        cq = c.empty(R, self.q_rank)
+        _chk(lib.pa_rms_norm_rows(proj.data_ptr(), proj.stride(0), 0, self.q_rank, c.model.eps, self.dq_gain.data_ptr(),
+                                  cq.data_ptr(), self.q_rank, R, c.elem, s), "pa_rms_norm_rows")
+        q = c.model._linear(cq, self.w_uq)
+        rope = c.rope_table(self.rot_dims, self.rot_base)
+        _chk(lib.pa_rope_rows(q.data_ptr(), q.stride(0), self.dim, self.qd, H, self.rot_dims, _cabi.ptr(rope), R, c.elem, s),
+             "pa_rope_rows")
+        pt = kv.page_table_
+        table = pt.device_data()
+        if self.own_kv:
+            _chk(lib.pa_latent_kv_append(kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_tiles_,
+                                         kv.total_pages_, kv.tile_size_, self.kv_rank, self.rot_dim, self.rot_dims,
+                                         proj.data_ptr(), proj.stride(0), self.c_off, self.dkv_gain.data_ptr(), c.model.eps,
+                                         _cabi.ptr(rope), b.row_slot.data_ptr(), b.row_pos.data_ptr(), R, c.elem, s),
+                 "pa_latent_kv_append")
+        ql = c.empty(R, H * self.kv_rank)
+        self._head_linear(c, q, q.stride(0), self.qd, self.w_uk, self.dim, self.kv_rank, ql)
+        lat = c.empty(R, H * self.kv_rank)
+        sms = c.model.sm_count
+        for kind, group in b.query_tiles(self.tile_tokens, self.mma_tokens, MMA_FROM).items():
+            if group is None:
+                continue
+            tiles, ntiles, longest = group
+            nsplit, ws = 1, None
+            ctas = ntiles * math.ceil(H / 32)
+            if kind == 2:
+                kernel_kind = 2
+            else:
+                kernel_kind = 0
+                if ctas < 2 * sms and longest > 512:      # too few CTAs for the chip over a long context: cut the keys
+                    nsplit = max(1, min(math.ceil(2 * sms / ctas), longest // 256, 64))
+            if nsplit > 1:
+                ws = c.empty(lib.pa_latent_attention_workspace_bytes(ntiles, H, self.kv_rank, nsplit), dtype=torch.uint8)
+            _chk(lib.pa_latent_attention(ql.data_ptr(), H * self.kv_rank, self.kv_rank, q.data_ptr() + self.dim * c.elem,
+                                         q.stride(0), self.qd, kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_,
+                                         pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, H,
+                                         self.kv_rank, self.rot_dim, self.scale, lat.data_ptr(), H * self.kv_rank,
+                                         self.kv_rank, c.elem, nsplit, kernel_kind, _cabi.ptr(ws),
+                                         ws.numel() if ws is not None else 0, s), "pa_latent_attention")
+        ov = c.empty(R, H * self.vdim)
+        self._head_linear(c, lat, H * self.kv_rank, self.kv_rank, self.w_uv, self.kv_rank, self.vdim, ov)
+        og = c.empty(R, H * self.vdim)
+        _chk(lib.pa_head_gate(ov.data_ptr(), H * self.vdim, self.vdim, proj.data_ptr() + self.g_off * c.elem, proj.stride(0),
+                              H, self.vdim, R, og.data_ptr(), c.elem, s), "pa_head_gate")
+        return c.model._linear(og, self.w_o)
+
+
+MIXERS = {"mingru": MinGRUMixer, "attention": DiffAttentionMixer, "latent_attention": LatentAttentionMixer}
 
 
 # --------------------------------------------------------------------------------------------------------- feed-forwards
+_GLU_ACT = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+_EXPERT_ACT = {"silu": 0, "relu": 1, "relu2": 2}
+
+
 class DenseFF:
+    """W_down act(W_up h) (gated=False, act 'gelu_erf'), or the gated form W_down (act(W_gate h) * (W_up h))."""
     kind = "dense"
 
-    def __init__(self, model, prefix, cfg, W):
-        self.w_up = model._weight(W[prefix + "up"])
+    def __init__(self, model, prefix, cfg, W, act="gelu_erf", gated=False):
+        self.gated, self.act = bool(gated), act
+        if (self.gated and act not in _GLU_ACT) or (not self.gated and act != "gelu_erf"):
+            raise ValueError(f"dense feed-forward: activation {act!r} is not served")
+        self.ff = int(W[prefix + "up"].shape[0])
+        self.w_up = model._weight(torch.cat([W[prefix + "gate"], W[prefix + "up"]], 0) if self.gated else W[prefix + "up"])
         self.w_down = model._weight(W[prefix + "down"])
 
     def forward(self, c, h):
         a = c.model._linear(h, self.w_up)
-        _chk(c.lib.pa_gelu_inplace(a.data_ptr(), a.numel(), c.elem, _cabi.stream()), "pa_gelu_inplace")
+        if self.gated:
+            gu, a = a, c.empty(c.R, self.ff)
+            _chk(c.lib.pa_act_mul(gu.data_ptr(), c.R, self.ff, _GLU_ACT[self.act], a.data_ptr(), c.elem, _cabi.stream()),
+                 "pa_act_mul")
+        else:
+            _chk(c.lib.pa_gelu_inplace(a.data_ptr(), a.numel(), c.elem, _cabi.stream()), "pa_gelu_inplace")
         return dict(dense=c.model._linear(a, self.w_down))
 
 
+_SCORE_FN = {"sigmoid": 0, "softmax": 1, "softmax_chosen": 2}
+
+
 class MoEFF:
-    """Routed experts: scores = sigmoid(router logits), the `top` largest, not renormalised, applied to the expert's
-    input; grouped matrix products over the pairs sorted by expert (csrc/moe_ops.cu); optional gated shared expert."""
+    """Routed experts over the pairs sorted by expert (grouped matrix products, csrc/moe_ops.cu).  Constants of a design:
+    score ('sigmoid' / 'softmax' over all experts, the `top` largest scores, or 'softmax_chosen': the `top` largest
+    logits, softmax over those only), an optional router bias ('<prefix>router.b'), weight_on ('input': the score scales
+    the expert's input row; 'output': the weighted sum of the experts' outputs), gated experts W_down(act(W_gate a) *
+    W_up a) or plain ones W_down act(W_up a), and an optional gated shared expert."""
     kind = "moe"
 
-    def __init__(self, model, prefix, cfg, W):
+    def __init__(self, model, prefix, cfg, W, score="sigmoid", weight_on="input", act="silu", gated=True):
         self.experts, self.top = int(cfg["router"]["experts"]), int(cfg["router"]["top"])
         self.ff = int(cfg["expert"]["ff"])
+        self.score_fn, self.weight_on, self.act, self.gated = _SCORE_FN[score], weight_on, _EXPERT_ACT[act], bool(gated)
+        if weight_on not in ("input", "output") or not 0 < self.top <= self.experts:
+            raise ValueError("routed feed-forward: bad constants")
         ex = lambda n: [W[f"{prefix}e{e}.{n}"] for e in range(self.experts)]  # noqa: E731
-        self.w_gate_up = model._weight_raw(torch.stack([torch.cat([g, u], 0) for g, u in zip(ex("gate"), ex("up"))]))
+        if self.gated:
+            self.w_gate_up = model._weight_raw(torch.stack([torch.cat([g, u], 0) for g, u in zip(ex("gate"), ex("up"))]))
+        else:
+            self.w_gate_up = model._weight_raw(torch.stack(ex("up")))
         self.w_down = model._weight_raw(torch.stack(ex("down")))
         self.w_router = model._f32(W[prefix + "router"])
+        self.b_router = model._f32(W[prefix + "router.b"]) if prefix + "router.b" in W else None
         self.shared = None
         if cfg.get("shared"):
             sp = prefix + "shared."
@@ -192,20 +355,22 @@ class MoEFF:
         sel_id, sel_w = c.empty(pairs, **i32), c.empty(pairs, **f32)
         sh = self.shared
         sgate = c.empty(R, **f32) if sh and sh["w_sg"] is not None else None
-        _chk(lib.pa_router_topk(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(sh["w_sg"]) if sgate is not None else None,
-                                R, wdt, self.experts, self.top, 0, 0, sel_id.data_ptr(), sel_w.data_ptr(),
-                                _cabi.ptr(sgate), c.elem, s), "pa_router_topk")
+        _chk(lib.pa_router_topk(h.data_ptr(), self.w_router.data_ptr(), _cabi.ptr(self.b_router),
+                                _cabi.ptr(sh["w_sg"]) if sgate is not None else None, R, wdt, self.experts, self.top,
+                                self.score_fn, 0, sel_id.data_ptr(), sel_w.data_ptr(), _cabi.ptr(sgate), c.elem, s),
+             "pa_router_topk")
         order = c.empty(pairs, **i32)
         meta = c.empty(lib.pa_moe_meta_ints(pairs, self.experts), **i32)
         _chk(lib.pa_moe_sort(sel_id.data_ptr(), pairs, self.experts, order.data_ptr(), meta.data_ptr(), s), "pa_moe_sort")
         act = c.empty(pairs, self.ff)
-        _chk(lib.pa_moe_gate_up(h.data_ptr(), h.stride(0), self.w_gate_up.data_ptr(), wdt, self.ff, self.experts,
-                                order.data_ptr(), sel_w.data_ptr(), self.top, meta.data_ptr(), pairs, act.data_ptr(),
-                                c.elem, s), "pa_moe_gate_up")
+        in_w = sel_w.data_ptr() if self.weight_on == "input" else None
+        _chk((lib.pa_moe_gate_up_act if self.gated else lib.pa_moe_up)(
+            h.data_ptr(), h.stride(0), self.w_gate_up.data_ptr(), wdt, self.ff, self.experts, order.data_ptr(), in_w,
+            self.top, meta.data_ptr(), pairs, self.act, act.data_ptr(), c.elem, s), "pa_moe_gate_up_act / pa_moe_up")
         routed = c.empty(pairs, wdt, **f32)
         _chk(lib.pa_moe_down(act.data_ptr(), self.w_down.data_ptr(), self.ff, wdt, self.experts, order.data_ptr(),
                              meta.data_ptr(), pairs, routed.data_ptr(), c.elem, s), "pa_moe_down")
-        out = dict(routed=routed, top=self.top)
+        out = dict(routed=routed, top=self.top, sel_w=sel_w if self.weight_on == "output" else None)
         if sh:
             gu = c.model._linear(h, sh["w_gate_up"])
             a = c.empty(R, sh["ff"])
@@ -216,13 +381,22 @@ class MoEFF:
 
 FEED_FORWARDS = {"dense": DenseFF, "moe": MoEFF}
 
+# What a design fixes: the wiring of a layer, and the constants its feed-forwards are built with (its mixers take
+# theirs from the layer's config).
+DESIGNS = {
+    "Megusun": dict(wiring="parallel", ff={"dense": dict(act="gelu_erf", gated=False),
+                                            "moe": dict(score="sigmoid", weight_on="input", act="silu", gated=True)}),
+    "Domilix": dict(wiring="post_norm", ff={"dense": dict(act="relu", gated=True),
+                                            "moe": dict(score="softmax_chosen", weight_on="output", act="relu2", gated=False)}),
+}
+
 
 class _Layer:
     pass
 
 
 class HybridDecoder:
-    ARCHITECTURES = ("Megusun",)
+    ARCHITECTURES = tuple(DESIGNS)
 
     def __init__(self, config, weights, dtype="bfloat16", *, max_tokens=4096, max_seqs=4, tile_size=16, device=None):
         from .seq_state import SequenceStateCache
@@ -233,7 +407,10 @@ class HybridDecoder:
         self.config = config
         self.width, self.vocab = int(config["width"]), int(config["vocab"])
         self.eps = float(config["norm"]["eps"])
+        self.design = DESIGNS[config.get("architecture", "Megusun")]
+        self.wiring = self.design["wiring"]
         self.mult = float(config.get("residual_mult", 1.0))
+        self.embed_scale = float((config.get("embedding") or {}).get("scale", 1.0))
         self.states = SequenceStateCache(max_seqs, max_tokens, tile_size, self.device)
         self._ws = None
         W = weights
@@ -241,14 +418,21 @@ class HybridDecoder:
             raise ValueError("embed does not match config vocab / width")
         self.embed = W["embed"].to(self.device, self.act_dtype).contiguous()
         self.head = self._weight(W["head"])
-        self.final_gain = float(W["final.norm"].to(torch.float32))
+        post = self.wiring == "post_norm"
+        self.final_gain = 1.0 if post else float(W["final.norm"].to(torch.float32))
+        self.final_gain_vec = self._f32(W["final.norm"].reshape(-1)) if post else None
         self.layers = []
         for i, lc in enumerate(config["layers"]):
             L = _Layer()
             p = f"l{i}."
-            L.gain = float(W[p + "norm1"].to(torch.float32))
-            L.shift = self._f32(W[p + "shift"]) if p + "shift" in W else None
-            L.prev = self.states.add_state(self.width) if L.shift is not None else None
+            if post:    # per-channel gains of the norms on the two sublayers' outputs
+                L.gain1 = self._f32(W[p + "norm1"].reshape(-1))
+                L.gain2 = self._f32(W[p + "norm2"].reshape(-1)) if lc.get("mlp") else None
+                L.shift = L.prev = None
+            else:
+                L.gain = float(W[p + "norm1"].to(torch.float32))
+                L.shift = self._f32(W[p + "shift"]) if p + "shift" in W else None
+                L.prev = self.states.add_state(self.width) if L.shift is not None else None
             if lc["type"] not in MIXERS:
                 raise ValueError(f"unknown mixer type {lc['type']!r}")
             L.mixer = MIXERS[lc["type"]](self, p + "mix.", lc.get("mixer") or {}, W)
@@ -257,7 +441,7 @@ class HybridDecoder:
             if mc:
                 if mc["kind"] not in FEED_FORWARDS:
                     raise ValueError(f"unknown feed-forward kind {mc['kind']!r}")
-                L.ff = FEED_FORWARDS[mc["kind"]](self, p + "mlp.", mc, W)
+                L.ff = FEED_FORWARDS[mc["kind"]](self, p + "mlp.", mc, W, **self.design["ff"][mc["kind"]])
             self.layers.append(L)
 
     @classmethod
@@ -305,9 +489,11 @@ class HybridDecoder:
         c = _Ctx(self, batch)
         lib, R, W, s = self._lib, batch.rows, self.width, _cabi.stream()
         x = torch.empty((R, W), dtype=torch.float32, device=self.device)
-        _chk(lib.pa_embedding_rows(self.embed.data_ptr(), c.elem, batch.ids.data_ptr(), R, W, self.vocab, x.data_ptr(), s),
-             "pa_embedding_rows")
-        for L in self.layers:
+        _chk(lib.pa_embedding_rows_scaled(self.embed.data_ptr(), c.elem, batch.ids.data_ptr(), R, W, self.vocab,
+                                          self.embed_scale, x.data_ptr(), s), "pa_embedding_rows_scaled")
+        if self.wiring == "post_norm":
+            self._post_norm_layers(c, x)
+        for L in self.layers if self.wiring == "parallel" else ():
             h = c.empty(R, W)
             hs = c.empty(R, W) if L.shift is not None else None
             _chk(lib.pa_rms_norm_shift(x.data_ptr(), R, W, self.eps, L.gain, None, _cabi.ptr(L.shift),
@@ -333,8 +519,34 @@ class HybridDecoder:
         else:
             n, xs = R, x
         hf = torch.empty((n, W), dtype=self.act_dtype, device=self.device)
-        _chk(lib.pa_rms_norm_shift(xs.data_ptr(), n, W, self.eps, self.final_gain, None, None, None, None, None,
-                                   hf.data_ptr(), None, c.elem, s), "pa_rms_norm_shift")
+        _chk(lib.pa_rms_norm_shift(xs.data_ptr(), n, W, self.eps, self.final_gain, _cabi.ptr(self.final_gain_vec), None, None,
+                                   None, None, hf.data_ptr(), None, c.elem, s), "pa_rms_norm_shift")
         return self._linear(hf, self.head, out_dtype=torch.float32)
+
+    def _post_norm_layers(self, c, x):
+        """x += N(mixer(x)), then x += N(ff(x)): the sublayers read the residual itself (rounded to the activation type
+        for the products in bfloat16; the float rows themselves in float32), the norm is on their output, and the
+        residual sum stays float.  pa_residual_add_norm leaves the next sublayer's operand as it updates x."""
+        lib, R, W, s = self._lib, c.R, self.width, _cabi.stream()
+        f32 = self.act_dtype == torch.float32
+        h = x
+        if not f32:
+            h = c.empty(R, W)
+            _chk(lib.pa_cast_rows(x.data_ptr(), R * W, h.data_ptr(), c.elem, s), "pa_cast_rows")
+        for L in self.layers:
+            mix = L.mixer.forward(c, h)
+            nxt = None if f32 else c.empty(R, W)
+            _chk(lib.pa_residual_add_norm(x.data_ptr(), R, W, self.eps, L.gain1.data_ptr(), mix.data_ptr(), None, None, 0,
+                                          _cabi.ptr(nxt), c.elem, s), "pa_residual_add_norm")
+            h = x if f32 else nxt
+            if L.ff is not None:
+                ff = L.ff.forward(c, h)
+                nxt = None if f32 else c.empty(R, W)
+                _chk(lib.pa_residual_add_norm(x.data_ptr(), R, W, self.eps, L.gain2.data_ptr(), _cabi.ptr(ff.get("dense")),
+                                              _cabi.ptr(ff.get("routed")), _cabi.ptr(ff.get("sel_w")), ff.get("top", 0),
+                                              _cabi.ptr(nxt), c.elem, s), "pa_residual_add_norm")
+                h = x if f32 else nxt
+            if self.layer_hook is not None:
+                self.layer_hook(x)
 
     layer_hook = None   # debugging aid: called with the float residual after every layer

@@ -39,6 +39,7 @@ class KVTileCache:
         self.key_buffer_ = self.value_buffer_ = None
         self.k_scales_ = self.v_scales_ = None
         self.tile_size_ = self.head_dim_ = self.value_dim_ = self.total_pages_ = 0
+        self.single_rows_ = False         # init(value_dim=0): no value pool
         self.evict_on_exhaustion = True   # the reference's LRU rule; False: a full pool raises
         self.page_table_ = PageTable(device)
         self.tile_to_page_map_ = OrderedDict()  # (beam, head, tile) -> page, LRU order (oldest first)
@@ -50,7 +51,9 @@ class KVTileCache:
     # ---- kv_tile_cache.cpp:18-24, 39-50 ------------------------------------------------
     def init(self, num_pages, tile_size, head_dim, value_dim=None):
         value_dim = head_dim if value_dim is None else value_dim
-        if min(num_pages, tile_size, head_dim, value_dim) <= 0:
+        # value_dim 0: a pool of single rows (attention through a latent: the values are columns of the key rows)
+        self.single_rows_ = int(value_dim) == 0
+        if min(num_pages, tile_size, head_dim) <= 0 or value_dim < 0:
             raise ValueError("KVTileCache.init: sizes must be positive")
         self.tile_size_, self.head_dim_, self.total_pages_ = int(tile_size), int(head_dim), int(num_pages)
         self.value_dim_ = int(value_dim)
@@ -75,8 +78,8 @@ class KVTileCache:
         shape = (self.total_pages_, self.tile_size_, self.head_dim_)
         dev = self._dev()
         self.key_buffer_ = torch.zeros(shape, dtype=_DTYPES[self.dtype], device=dev)
-        self.value_buffer_ = torch.zeros(shape[:2] + (self.value_dim_ or self.head_dim_,), dtype=_DTYPES[self.dtype],
-                                         device=dev)
+        self.value_buffer_ = None if self.single_rows_ else torch.zeros(
+            shape[:2] + (self.value_dim_ or self.head_dim_,), dtype=_DTYPES[self.dtype], device=dev)
         if self.dtype == "i8":
             self.k_scales_ = torch.ones(shape[:2], dtype=torch.float32, device=dev)
             self.v_scales_ = torch.ones(shape[:2], dtype=torch.float32, device=dev)
