@@ -247,7 +247,7 @@ def bench_kernels(s, dev):
         wr = torch.randn(E, W, device=dev) / math.sqrt(W)
         sel_id, sel_w = torch.empty(pairs, device=dev, dtype=i32), torch.empty(pairs, device=dev)
         sg, sgw = torch.empty(R, device=dev), torch.randn(W, device=dev)
-        rec(f"router_topk/{tag}", timed(lambda: lib.pa_router_topk(hb.data_ptr(), wr.data_ptr(), sgw.data_ptr(), R, W, E, top,
+        rec(f"router_topk/{tag}", timed(lambda: lib.pa_router_topk(hb.data_ptr(), wr.data_ptr(), None, sgw.data_ptr(), R, W, E, top,
                                                                    0, 0, sel_id.data_ptr(), sel_w.data_ptr(), sg.data_ptr(), 2, st())),
             bytes_=R * W * 2)
         order = torch.empty(pairs, device=dev, dtype=i32)

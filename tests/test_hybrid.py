@@ -469,7 +469,7 @@ def test_kernels_alone_against_the_oracle_functions():
     want = R.moe_ff(h.double(), wr.double(), [tuple(t.double() for t in e) for e in ex], top)
     hd, wrd = h.to(dev), wr.to(dev)
     sel_id, sel_w = torch.empty(rows * top, dtype=torch.int32, device=dev), torch.empty(rows * top, device=dev)
-    _cabi.check(lib.pa_router_topk(hd.data_ptr(), wrd.data_ptr(), None, rows, wdt, E, top, 0, 0, sel_id.data_ptr(),
+    _cabi.check(lib.pa_router_topk(hd.data_ptr(), wrd.data_ptr(), None, None, rows, wdt, E, top, 0, 0, sel_id.data_ptr(),
                                    sel_w.data_ptr(), None, 4, s()), "router")
     sc = torch.sigmoid(h.double() @ wr.double().T)
     tv, ti = sc.topk(top, -1)
@@ -555,7 +555,7 @@ def test_router_scores_and_shared_gate(width, experts, top, elem):
     hd, wrd, wgd = h.to(dev), wr.to(dev), wg.to(dev)
     sel_id, sel_w = torch.empty(rows * top, dtype=torch.int32, device=dev), torch.empty(rows * top, device=dev)
     gate = torch.empty(rows, device=dev)
-    _cabi.check(lib.pa_router_topk(hd.data_ptr(), wrd.data_ptr(), wgd.data_ptr(), rows, width, experts, top, 0, 0,
+    _cabi.check(lib.pa_router_topk(hd.data_ptr(), wrd.data_ptr(), None, wgd.data_ptr(), rows, width, experts, top, 0, 0,
                                    sel_id.data_ptr(), sel_w.data_ptr(), gate.data_ptr(), elem, s()), "router")
     assert torch.equal(sel_id.cpu().view(rows, top).long(), ti)
     assert (sel_w.cpu().view(rows, top).double() - tv).abs().max() < 1e-5
