@@ -195,11 +195,12 @@ struct LatentAttnParams {
     void* out;                  // (row, head, d) at row * o_rs + head * o_hs + d, d < kv_rank
     int64_t o_rs, o_hs;
     int nsplit;
-    float* partial;             // nsplit > 1: [(tile, chunk, split, row)][2 + kv_rank]
+    float* partial;             // nsplit > 1: [(tile, chunk, split, row)][2 + kv_rank], m in natural-log units
+    int cta_rows;               // (token, head) rows per CTA: kLaRows (float kernel) or kLmRows (tensor-core kernel)
 };
 
-__device__ __forceinline__ void la_geometry(int heads, int& hc, int& nchunk) {
-    hc = heads < kLaRows ? heads : kLaRows;
+__host__ __device__ __forceinline__ void la_geometry(int heads, int cta_rows, int& hc, int& nchunk) {
+    hc = heads < cta_rows ? heads : cta_rows;
     nchunk = (heads + hc - 1) / hc;
 }
 
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(kLaWarps * 32) latent_attention_kernel(const L
     __shared__ int64_t page_row[kLaKeys];
 
     int hc, nchunk;
-    la_geometry(p.heads, hc, nchunk);
+    la_geometry(p.heads, kLaRows, hc, nchunk);
     const int bq = kLaRows / hc;
     const int* tile = p.tiles + 4 * blockIdx.x;
     const int row0 = tile[0], ntok = tile[1], slot = tile[2], pos0 = tile[3];
@@ -336,18 +337,17 @@ __global__ void __launch_bounds__(kLaWarps * 32) latent_attention_kernel(const L
 template <typename T, int NV>
 __global__ void __launch_bounds__(kLaWarps * 32) latent_attention_merge_kernel(const LatentAttnParams p) {
     int hc, nchunk;
-    la_geometry(p.heads, hc, nchunk);
-    const int bq = kLaRows / hc;
+    la_geometry(p.heads, p.cta_rows, hc, nchunk);
+    const int bq = p.cta_rows / hc;
     const int* tile = p.tiles + 4 * blockIdx.x;
     const int row0 = tile[0], ntok = tile[1];
     const int chunk = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r = 0; r < kLaRpw; ++r) {
-        const int row = warp * kLaRpw + r;
+    for (int row = warp; row < p.cta_rows; row += kLaWarps) {
         const int tok = row / hc, hh = chunk * hc + row % hc;
         if (!(tok < bq && tok < ntok && hh < p.heads)) continue;
-        const int64_t zs = (int64_t)kLaRows * (2 + p.kv_rank);
-        const float* base = p.partial + (((int64_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit * kLaRows + row) * (2 + p.kv_rank);
+        const int64_t zs = (int64_t)p.cta_rows * (2 + p.kv_rank);
+        const float* base = p.partial + (((int64_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit * p.cta_rows + row) * (2 + p.kv_rank);
         float M = -INFINITY;
         for (int z = 0; z < p.nsplit; ++z) M = fmaxf(M, base[z * zs]);
         float l = 0.f, acc[NV];
@@ -378,8 +378,7 @@ static int la_launch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int hc, nchunk;
-    hc = p.heads < kLaRows ? p.heads : kLaRows;
-    nchunk = (p.heads + hc - 1) / hc;
+    la_geometry(p.heads, kLaRows, hc, nchunk);
     dim3 grid((unsigned)ntiles, (unsigned)nchunk, (unsigned)p.nsplit);
     kern<<<grid, kLaWarps * 32, smem, st>>>(p);
     if (p.nsplit > 1) {
@@ -397,6 +396,266 @@ static int la_dispatch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
     if (nv <= 4) return la_launch<T, 4>(p, ntiles, st);
     if (nv <= 8) return la_launch<T, 8>(p, ntiles, st);
     if (nv <= 16) return la_launch<T, 16>(p, ntiles, st);
+    return PA_ERR_UNSUPPORTED;
+}
+
+// ---- attention on the tensor cores (bfloat16) -------------------------------------------------------------------------
+// One CTA = up to 64 (token, head) rows that read the same pool rows: 64 / hc consecutive tokens of one portion x hc =
+// min(64, heads) heads (a decoded token: its heads alone).  8 warps: warp w owns the 16 rows (w & 3) and the latent
+// columns of half (w >> 2) of the output, so the accumulators of a 512-wide latent are 128 registers per thread.  Per
+// step 64 keys are located through the page table and brought in with 16-byte cp.async copies into one of two buffers
+// (the copies of step t + 1 fly while step t is multiplied); the staged rows serve both products: S = Q K^T over all
+// kv_rank + rot_dim columns (mma.sync m16n8k16, bfloat16 operands, float accumulators; both warps of a row group compute
+// the scores of their 16 rows, which costs less than handing the weights across), and O += P V with V = the first
+// kv_rank columns of the same rows, read transposed by ldmatrix.  Scores, the running maximum, the exponentials and
+// their sum are float; the weights enter the second product rounded to bfloat16, like every other matrix operand of
+// this precision.  KVR and ROT are the PADDED sizes: the real kv_rank / rot_dim values (multiples of 8) sit at the start
+// of their columns in shared memory, the rest is zero, and 16-wide steps that are all padding are skipped.  nsplit > 1
+// cuts the key steps into parts whose (m, l, acc) go to the float kernel's partial layout and merge kernel.
+constexpr int kLmRows = 64, kLmKeys = 64, kLmThreads = 256, kLmPad = 8;
+
+template <int KVR, int ROT>
+__global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(const LatentAttnParams p) {
+    constexpr int KD = KVR + ROT, KS = KD + kLmPad, NT = KVR / 16;     // NT 8-column tiles per warp (half of KVR)
+    extern __shared__ __align__(16) unsigned char lm_smem[];
+    bf16_t* Qs = reinterpret_cast<bf16_t*>(lm_smem);                   // [64][KS]
+    bf16_t* Ks = Qs + kLmRows * KS;                                     // [2][64][KS]
+    __shared__ int key_ok[2][kLmKeys];
+
+    int hc, nchunk;
+    la_geometry(p.heads, kLmRows, hc, nchunk);
+    const int bq = kLmRows / hc;
+    const int* tile = p.tiles + 4 * blockIdx.x;
+    const int row0 = tile[0], ntok = tile[1], slot = tile[2], pos0 = tile[3];
+    const int chunk = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rg = warp & 3, ch = warp >> 2;
+    const int kv_rank = p.kv_rank, rot_dim = p.rot_dim, kd = kv_rank + rot_dim;
+    const bf16_t* pool = static_cast<const bf16_t*>(p.pool);
+    const int32_t* trow = p.table + (int64_t)slot * p.num_tiles;
+    const int total = pos0 + ntok;
+    const int nkt = (total + kLmKeys - 1) / kLmKeys;
+    const int per = (nkt + p.nsplit - 1) / p.nsplit;
+    const int kt0 = blockIdx.z * per, kt1 = min(nkt, kt0 + per);
+
+    // queries: piece v of a row is 8 columns of the latent part (v * 8 < KVR) or of the rotated part
+    for (int c = tid; c < kLmRows * (KD / 8); c += kLmThreads) {
+        const int r = c / (KD / 8), v = c % (KD / 8);
+        const int tok = r / hc, hh = chunk * hc + r % hc;
+        const bool row_ok = tok < bq && tok < ntok && hh < p.heads;
+        const int col = v * 8;
+        const bf16_t* src = pool;
+        bool ok = false;
+        if (row_ok && col < KVR && col < kv_rank) {
+            src = static_cast<const bf16_t*>(p.q_lat) + (int64_t)(row0 + tok) * p.ql_rs + (int64_t)hh * p.ql_hs + col;
+            ok = true;
+        } else if (row_ok && col >= KVR && col - KVR < rot_dim) {
+            src = static_cast<const bf16_t*>(p.q_rot) + (int64_t)(row0 + tok) * p.qr_rs + (int64_t)hh * p.qr_hs + col - KVR;
+            ok = true;
+        }
+        cp_async_16(smem_u32(Qs + r * KS + col), src, ok);
+    }
+    auto pool_row = [&](int j) -> int64_t {
+        if (j < total && j / p.tile_size < p.num_tiles) {
+            const int page = trow[j / p.tile_size];
+            if (page >= 0 && page < p.total_pages) return (int64_t)page * p.tile_size + j % p.tile_size;
+        }
+        return -1;
+    };
+    // four threads per key: one page look-up per thread and step; a thread copies every fourth 16-byte piece of its row
+    auto load_tile = [&](int kt, int buf) {
+        const int key = tid >> 2, q4 = tid & 3;
+        const int64_t pr = pool_row(kt * kLmKeys + key);
+        if (q4 == 0) key_ok[buf][key] = pr >= 0;
+        bf16_t* dst = Ks + (buf * kLmKeys + key) * KS;
+        const bf16_t* src = pool + (pr >= 0 ? pr * kd : 0);
+#pragma unroll
+        for (int i = 0; i < KD / 32; ++i) {
+            const int col = (q4 + 4 * i) * 8;
+            const bool lat = col < KVR;
+            const bool ok = pr >= 0 && (lat ? col < kv_rank : col - KVR < rot_dim);
+            cp_async_16(smem_u32(dst + col), ok ? src + (lat ? col : kv_rank + col - KVR) : pool, ok);
+        }
+    };
+    if (kt0 < kt1) load_tile(kt0, 0);
+    cp_async_commit();
+
+    float o[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[t][c] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    int rpos[2];
+    bool any_row = false;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = rg * 16 + (lane >> 2) + 8 * i;
+        const int tok = r / hc, hh = chunk * hc + r % hc;
+        rpos[i] = (tok < bq && tok < ntok && hh < p.heads) ? pos0 + tok : -1;
+        any_row |= rpos[i] >= 0;
+    }
+    const bool active = __any_sync(0xffffffffu, any_row);        // this warp has rows with a query
+    const float sc = p.scale * 1.4426950408889634f;
+
+    for (int kt = kt0; kt < kt1; ++kt) {
+        const int buf = (kt - kt0) & 1, c0 = kt * kLmKeys;
+        if (kt + 1 < kt1) load_tile(kt + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (active) {
+            float s[8][4];
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[t][c] = 0.f;
+#pragma unroll 4
+            for (int ks = 0; ks < KD; ks += 16) {
+                if (ks < KVR ? ks >= kv_rank : ks - KVR >= rot_dim) continue;      // all padding
+                uint32_t a[4];
+                ldsm_x4(smem_u32(Qs + (rg * 16 + (lane & 15)) * KS + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(smem_u32(Ks + (buf * kLmKeys + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + ks + ((lane >> 3) & 1) * 8),
+                            b0, b1, b2, b3);
+                    mma_bf16_16816(s[2 * np], a, b0, b1);
+                    mma_bf16_16816(s[2 * np + 1], a, b2, b3);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int col = t * 8 + 2 * (lane & 3);
+                const int2 okk = *reinterpret_cast<const int2*>(&key_ok[buf][col]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int i = c >> 1;
+                    const bool vis = ((c & 1) ? okk.y : okk.x) && c0 + col + (c & 1) <= rpos[i];
+                    s[t][c] = vis ? s[t][c] * sc : -INFINITY;
+                    mx[i] = fmaxf(mx[i], s[t][c]);
+                }
+            }
+            float ref[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float mn = fmaxf(m[i], mx[i]);
+                ref[i] = mn == -INFINITY ? 0.f : mn;
+                const float corr = exp2f(m[i] - ref[i]);         // m = -inf: 0 (nothing accumulated yet)
+                m[i] = mn;
+                l[i] *= corr;
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    o[t][2 * i] *= corr;
+                    o[t][2 * i + 1] *= corr;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    s[t][c] = exp2f(s[t][c] - ref[c >> 1]);
+                    l[c >> 1] += s[t][c];
+                }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                uint32_t a[4];
+                a[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
+                a[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+                a[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                a[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int np = 0; np < NT / 2; ++np) {
+                    const int col0 = ch * (KVR / 2) + np * 16;
+                    if (col0 >= kv_rank) continue;               // all padding
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_trans(smem_u32(Ks + (buf * kLmKeys + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + col0 + (lane >> 4) * 8),
+                                  b0, b1, b2, b3);
+                    mma_bf16_16816(o[2 * np], a, b0, b1);
+                    mma_bf16_16816(o[2 * np + 1], a, b2, b3);
+                }
+            }
+        }
+        __syncthreads();                                         // this buffer is free for the copies of step kt + 2
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = rg * 16 + (lane >> 2) + 8 * i;
+        if (rpos[i] < 0) continue;
+        const int tok = r / hc, hh = chunk * hc + r % hc;
+        if (p.nsplit > 1) {
+            float* dst = p.partial + ((((int64_t)blockIdx.x * gridDim.y + blockIdx.y) * p.nsplit + blockIdx.z) * kLmRows + r) *
+                                         (2 + kv_rank);
+            if (ch == 0 && (lane & 3) == 0) { dst[0] = m[i] * 0.6931471805599453f; dst[1] = l[i]; }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const int col = ch * (KVR / 2) + t * 8 + 2 * (lane & 3);
+                if (col < kv_rank) { dst[2 + col] = o[t][2 * i]; dst[2 + col + 1] = o[t][2 * i + 1]; }
+            }
+        } else {
+            const float inv = 1.0f / l[i];
+            bf16_t* dst = static_cast<bf16_t*>(p.out) + (int64_t)(row0 + tok) * p.o_rs + (int64_t)hh * p.o_hs;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const int col = ch * (KVR / 2) + t * 8 + 2 * (lane & 3);
+                if (col < kv_rank) *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16x2(o[t][2 * i] * inv, o[t][2 * i + 1] * inv);
+            }
+        }
+    }
+}
+
+template <int NV>
+static int lm_merge(const LatentAttnParams& p, int ntiles, int nchunk, cudaStream_t st) {
+    latent_attention_merge_kernel<bf16_t, NV><<<dim3((unsigned)ntiles, (unsigned)nchunk), kLaWarps * 32, 0, st>>>(p);
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+template <int KVR, int ROT>
+static int lm_launch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
+    const size_t smem = (size_t)3 * kLmRows * (KVR + ROT + kLmPad) * sizeof(bf16_t);
+    if (smem > (size_t)device_info().max_smem_optin) return PA_ERR_UNSUPPORTED;
+    auto kern = latent_attention_mma_kernel<KVR, ROT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    int hc, nchunk;
+    la_geometry(p.heads, kLmRows, hc, nchunk);
+    kern<<<dim3((unsigned)ntiles, (unsigned)nchunk, (unsigned)p.nsplit), kLmThreads, smem, st>>>(p);
+    if (p.nsplit > 1) {
+        const int nv = (p.kv_rank + 31) / 32;
+        if (nv <= 1) return lm_merge<1>(p, ntiles, nchunk, st);
+        if (nv <= 2) return lm_merge<2>(p, ntiles, nchunk, st);
+        if (nv <= 4) return lm_merge<4>(p, ntiles, nchunk, st);
+        if (nv <= 8) return lm_merge<8>(p, ntiles, nchunk, st);
+        return lm_merge<16>(p, ntiles, nchunk, st);
+    }
+    PA_RETURN_LAUNCH_STATUS();
+}
+
+static bool lm_shape_ok(int kv_rank, int rot_dim) {
+    return kv_rank % 8 == 0 && kv_rank >= 8 && kv_rank <= 512 && rot_dim % 8 == 0 && rot_dim <= 64;
+}
+
+// PA_ERR_UNSUPPORTED: this shape or these pointers stay on the float kernel
+static int lm_dispatch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
+    if (!lm_shape_ok(p.kv_rank, p.rot_dim)) return PA_ERR_UNSUPPORTED;
+    if (p.ql_rs % 8 || p.ql_hs % 8 || p.o_rs % 2 || p.o_hs % 2) return PA_ERR_UNSUPPORTED;
+    if (p.rot_dim && (p.qr_rs % 8 || p.qr_hs % 8 || (uintptr_t)p.q_rot % 16)) return PA_ERR_UNSUPPORTED;
+    if ((uintptr_t)p.q_lat % 16 || (uintptr_t)p.pool % 16 || (uintptr_t)p.out % 4) return PA_ERR_UNSUPPORTED;
+    const int kp = p.kv_rank <= 64 ? 64 : p.kv_rank <= 128 ? 128 : p.kv_rank <= 256 ? 256 : 512;
+    const int rp = p.rot_dim <= 32 ? 32 : 64;
+#define PA_LM_CASE(K, R) if (kp == K && rp == R) return lm_launch<K, R>(p, ntiles, st)
+    PA_LM_CASE(64, 32); PA_LM_CASE(64, 64); PA_LM_CASE(128, 32); PA_LM_CASE(128, 64);
+    PA_LM_CASE(256, 32); PA_LM_CASE(256, 64); PA_LM_CASE(512, 32); PA_LM_CASE(512, 64);
+#undef PA_LM_CASE
     return PA_ERR_UNSUPPORTED;
 }
 
@@ -481,8 +740,15 @@ PA_API int pa_latent_attention_tile_tokens(int heads) {
 
 PA_API size_t pa_latent_attention_workspace_bytes(int num_q_tiles, int heads, int kv_rank, int nsplit) {
     if (nsplit <= 1 || num_q_tiles <= 0 || heads <= 0 || kv_rank <= 0) return 0;
-    const int hc = heads < kLaRows ? heads : kLaRows, nchunk = (heads + hc - 1) / hc;
-    return (size_t)num_q_tiles * nchunk * nsplit * kLaRows * (2 + kv_rank) * sizeof(float);
+    // the larger of the two kernels' geometries (CTA rows x head chunks), so one size serves either tile kind
+    size_t most = 0;
+    for (int rows : {kLaRows, kLmRows}) {
+        int hc, nchunk;
+        la_geometry(heads, rows, hc, nchunk);
+        const size_t n = (size_t)nchunk * rows;
+        most = n > most ? n : most;
+    }
+    return (size_t)num_q_tiles * nsplit * most * (2 + kv_rank) * sizeof(float);
 }
 
 PA_API int pa_latent_attention(const void* d_q_lat, int64_t ql_row_stride, int64_t ql_head_stride, const void* d_q_rot,
@@ -503,13 +769,15 @@ PA_API int pa_latent_attention(const void* d_q_lat, int64_t ql_row_stride, int64
     p.pool = d_pool; p.table = d_table; p.num_slots = num_slots; p.num_tiles = num_tiles; p.total_pages = total_pages;
     p.tile_size = tile_size; p.tiles = d_q_tiles; p.heads = heads; p.kv_rank = kv_rank; p.rot_dim = rot_dim; p.scale = scale;
     p.out = d_out; p.o_rs = o_row_stride; p.o_hs = o_head_stride; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace);
+    p.cta_rows = tile_kind == 2 ? kLmRows : kLaRows;
     if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
+    if (tile_kind == 2) return elem == 2 ? lm_dispatch(p, num_q_tiles, as_stream(stream)) : PA_ERR_UNSUPPORTED;
     if (tile_kind != 0) return PA_ERR_UNSUPPORTED;
     if (elem == 4) return la_dispatch<float>(p, num_q_tiles, as_stream(stream));
     return la_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));
 }
 
 PA_API int pa_latent_attention_mma_tile_tokens(int heads, int kv_rank, int rot_dim, int elem) {
-    (void)heads; (void)kv_rank; (void)rot_dim; (void)elem;
-    return 0;
+    if (heads <= 0 || elem != 2 || !lm_shape_ok(kv_rank, rot_dim)) return 0;
+    return kLmRows / (heads < kLmRows ? heads : kLmRows);
 }

@@ -228,12 +228,21 @@ class LatentAttentionMixer:
                 raise ValueError(f"{prefix}: kv_rank, rot_dim and rotation must equal those of layer {j}")
             self.kv = src.kv
         self.tile_tokens = model._lib.pa_latent_attention_tile_tokens(H)
-        self.mma_tokens = model._lib.pa_latent_attention_mma_tile_tokens(H, self.kv_rank, self.rot_dim, _ELEM[model.act_dtype])
+        # bfloat16 with 16-byte aligned query parts: every tile (portions and decoded tokens) runs on the tensor cores
+        self.mma_tokens = 0
+        if self.dim % 8 == 0 and qd % 8 == 0:
+            self.mma_tokens = model._lib.pa_latent_attention_mma_tile_tokens(H, self.kv_rank, self.rot_dim, _ELEM[model.act_dtype])
 
-    def _head_linear(self, c, x, x_rs, x_hs, w, K, N, out, x_off=0):
-        H = self.heads
-        _chk(c.lib.pa_head_linear(x.data_ptr() + x_off * c.elem, x_rs, x_hs, w.data_ptr(), H, K, N, c.R, out.data_ptr(),
-                                  H * N, N, c.elem, _cabi.stream()), "pa_head_linear")
+    def _head_linear(self, c, x, x_rs, x_hs, w, K, N):
+        """out[h, r, :] = x[r, h, :K] . w[h] for every head: [H, R, N] (row stride N, head stride R * N).  bfloat16: the
+        vendor's batched product on the strided view; float32: the IEEE FMA kernel."""
+        H, R = self.heads, c.R
+        if c.elem == 2:
+            return torch.bmm(torch.as_strided(x, (H, R, K), (x_hs, x_rs, 1)), w)
+        out = c.empty(H, R, N)
+        _chk(c.lib.pa_head_linear(x.data_ptr(), x_rs, x_hs, w.data_ptr(), H, K, N, R, out.data_ptr(), N, R * N, c.elem,
+                                  _cabi.stream()), "pa_head_linear")
+        return out
 
     def forward(self, c, h):
         b, lib, kv, s, R, H = c.batch, c.lib, self.kv, _cabi.stream(), c.R, self.heads
@@ -253,34 +262,30 @@ class LatentAttentionMixer:
                                          proj.data_ptr(), proj.stride(0), self.c_off, self.dkv_gain.data_ptr(), c.model.eps,
                                          _cabi.ptr(rope), b.row_slot.data_ptr(), b.row_pos.data_ptr(), R, c.elem, s),
                  "pa_latent_kv_append")
-        ql = c.empty(R, H * self.kv_rank)
-        self._head_linear(c, q, q.stride(0), self.qd, self.w_uk, self.dim, self.kv_rank, ql)
-        lat = c.empty(R, H * self.kv_rank)
+        kvr = self.kv_rank
+        ql = self._head_linear(c, q, q.stride(0), self.qd, self.w_uk, self.dim, kvr)          # [H, R, kv_rank]
+        lat = c.empty(H, R, kvr)
         sms = c.model.sm_count
-        for kind, group in b.query_tiles(self.tile_tokens, self.mma_tokens, MMA_FROM).items():
+        mma = self.mma_tokens > 0
+        rows_per_cta = 64 if mma else 32
+        for _kind, group in b.query_tiles(self.mma_tokens if mma else self.tile_tokens).items():
             if group is None:
                 continue
             tiles, ntiles, longest = group
             nsplit, ws = 1, None
-            ctas = ntiles * math.ceil(H / 32)
-            if kind == 2:
-                kernel_kind = 2
-            else:
-                kernel_kind = 0
-                if ctas < 2 * sms and longest > 512:      # too few CTAs for the chip over a long context: cut the keys
-                    nsplit = max(1, min(math.ceil(2 * sms / ctas), longest // 256, 64))
+            ctas = ntiles * math.ceil(H / rows_per_cta)
+            if ctas < 2 * sms and longest > 512:          # too few CTAs for the chip over a long context: cut the keys
+                nsplit = max(1, min(math.ceil(2 * sms / ctas), longest // 256, 64))
             if nsplit > 1:
-                ws = c.empty(lib.pa_latent_attention_workspace_bytes(ntiles, H, self.kv_rank, nsplit), dtype=torch.uint8)
-            _chk(lib.pa_latent_attention(ql.data_ptr(), H * self.kv_rank, self.kv_rank, q.data_ptr() + self.dim * c.elem,
-                                         q.stride(0), self.qd, kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_,
-                                         pt.num_tiles_, kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, H,
-                                         self.kv_rank, self.rot_dim, self.scale, lat.data_ptr(), H * self.kv_rank,
-                                         self.kv_rank, c.elem, nsplit, kernel_kind, _cabi.ptr(ws),
-                                         ws.numel() if ws is not None else 0, s), "pa_latent_attention")
-        ov = c.empty(R, H * self.vdim)
-        self._head_linear(c, lat, H * self.kv_rank, self.kv_rank, self.w_uv, self.kv_rank, self.vdim, ov)
+                ws = c.empty(lib.pa_latent_attention_workspace_bytes(ntiles, H, kvr, nsplit), dtype=torch.uint8)
+            _chk(lib.pa_latent_attention(ql.data_ptr(), kvr, R * kvr, q.data_ptr() + self.dim * c.elem, q.stride(0), self.qd,
+                                         kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_tiles_,
+                                         kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, H, kvr, self.rot_dim,
+                                         self.scale, lat.data_ptr(), kvr, R * kvr, c.elem, nsplit, 2 if mma else 0,
+                                         _cabi.ptr(ws), ws.numel() if ws is not None else 0, s), "pa_latent_attention")
+        ov = self._head_linear(c, lat, kvr, R * kvr, self.w_uv, kvr, self.vdim)               # [H, R, vdim]
         og = c.empty(R, H * self.vdim)
-        _chk(lib.pa_head_gate(ov.data_ptr(), H * self.vdim, self.vdim, proj.data_ptr() + self.g_off * c.elem, proj.stride(0),
+        _chk(lib.pa_head_gate(ov.data_ptr(), self.vdim, R * self.vdim, proj.data_ptr() + self.g_off * c.elem, proj.stride(0),
                               H, self.vdim, R, og.data_ptr(), c.elem, s), "pa_head_gate")
         return c.model._linear(og, self.w_o)
 

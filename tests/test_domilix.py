@@ -365,7 +365,8 @@ def test_greedy_generation_through_the_scheduler(dtype):
         else:
             chosen = torch.tensor([logits[t, o[t + 1]] for t in range(len(p) - 1, len(o) - 1)])
             best = logits[len(p) - 1:len(o) - 1].max(-1).values
-            assert float((best - chosen).max()) < 0.25              # the chosen token is (nearly) the oracle's best
+            assert float((best - chosen).max()) < 0.4               # the chosen token is (nearly) the oracle's best: two
+            #                                                         bfloat16 logits, each off by up to ~0.15 here
 
 
 @pytest.mark.gpu
@@ -572,3 +573,61 @@ def test_gated_relu_product_kernel(elem):
         cabi.check(lib.pa_act_mul(gud.data_ptr(), 37, 19, act, out.data_ptr(), elem, s()), "act_mul")
         want = fn(gu.double()[:, :19]) * gu.double()[:, 19:]
         assert (out.cpu().double() - want).abs().max() < (1e-5 if elem == 4 else 3e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,kv_rank,rot_dim,tile_size", [(5, 72, 24, 16), (16, 512, 64, 64), (3, 136, 8, 16), (70, 40, 0, 16),
+                                                             (1, 8, 16, 32)])
+def test_latent_attention_kernels_alone(heads, kv_rank, rot_dim, tile_size):
+    """pa_latent_attention on a pool with scattered pages: the float kernel (float and bfloat16 rows) and the tensor-core
+    kernel, portions of several lengths and single tokens over short and long contexts, with and without split keys,
+    latent widths that are not a power of two, more heads than a CTA has rows, no rotated part."""
+    cabi, lib, dev, s = _lib()
+    g = torch.Generator().manual_seed(heads * 1000 + kv_rank)
+    kd = kv_rank + rot_dim
+    # (slot, tokens held before, new tokens)
+    seqs = [(0, 0, 70), (1, 300, 1), (2, 129, 33), (3, 63, 2), (4, 700, 1)]
+    ntiles = 64
+    pages_needed = sum((before + n + tile_size - 1) // tile_size for _s, before, n in seqs)
+    perm = torch.randperm(pages_needed + 3, generator=g).tolist()
+    table = torch.full((5, ntiles), -1, dtype=torch.int32)
+    pool = torch.randn(pages_needed + 3, tile_size, kd, generator=g)
+    used = 0
+    for slot, before, n in seqs:
+        for t in range((before + n + tile_size - 1) // tile_size):
+            table[slot, t] = perm[used]
+            used += 1
+    R_ = sum(n for _s, _b, n in seqs)
+    ql = torch.randn(R_, heads, kv_rank, generator=g) * 0.3
+    qr = torch.randn(R_, heads, max(rot_dim, 1), generator=g) * 0.3
+    scale = 0.35
+    for elem, kind in ((4, 0), (2, 0), (2, 2)):
+        dt = torch.float32 if elem == 4 else torch.bfloat16
+        if kind == 2 and not lib.pa_latent_attention_mma_tile_tokens(heads, kv_rank, rot_dim, elem):
+            continue
+        tt = lib.pa_latent_attention_mma_tile_tokens(heads, kv_rank, rot_dim, elem) if kind == 2 else lib.pa_latent_attention_tile_tokens(heads)
+        poold, qld, qrd, tabled = pool.to(dt).to(dev), ql.to(dt).to(dev), qr.to(dt).to(dev), table.to(dev)
+        P, QL, QR = poold.cpu().double(), qld.cpu().double(), qrd.cpu().double()
+        want = torch.zeros(R_, heads, kv_rank, dtype=torch.float64)
+        tiles, r0 = [], 0
+        for slot, before, n in seqs:
+            keys = torch.stack([P[table[slot, j // tile_size], j % tile_size] for j in range(before + n)])
+            for t in range(n):
+                vis = keys[:before + t + 1]
+                sc = QL[r0 + t] @ vis[:, :kv_rank].T
+                if rot_dim:
+                    sc = sc + QR[r0 + t][:, :rot_dim] @ vis[:, kv_rank:].T
+                want[r0 + t] = torch.softmax(sc * scale, -1) @ vis[:, :kv_rank]
+            for o in range(0, n, tt):
+                tiles.append((r0 + o, min(tt, n - o), slot, before + o))
+            r0 += n
+        td = torch.tensor(tiles, dtype=torch.int32).to(dev)
+        for nsplit in (1, 3):
+            out = torch.zeros(R_, heads, kv_rank, dtype=dt, device=dev)
+            ws = torch.empty(max(1, lib.pa_latent_attention_workspace_bytes(len(tiles), heads, kv_rank, nsplit)), dtype=torch.uint8, device=dev)
+            cabi.check(lib.pa_latent_attention(qld.data_ptr(), heads * kv_rank, kv_rank, qrd.data_ptr(), qrd.stride(0), qrd.stride(1),
+                                               poold.data_ptr(), tabled.data_ptr(), 5, ntiles, poold.shape[0], tile_size, td.data_ptr(),
+                                               len(tiles), heads, kv_rank, rot_dim, scale, out.data_ptr(), heads * kv_rank, kv_rank,
+                                               elem, nsplit, kind, ws.data_ptr(), ws.numel(), s()), "latent_attention")
+            err = (out.cpu().double() - want).abs().max().item()
+            assert err < (2e-5 if elem == 4 else 2e-2), (elem, kind, nsplit, err)
