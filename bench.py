@@ -25,6 +25,8 @@ extra  = the other BASELINE.json configurations under the same clock (benchmarks
          stand-alone peer-memory exchange, and the NCCL all-gather form).  --no-extra skips them.
 --hybrid: a different workload altogether (benchmarks/hybrid.py): the config-driven hybrid stack against CUDADecoder at
          equal size; the default workload and its JSON contract are untouched by it.
+--latent: likewise (benchmarks/latent.py): the same stack serving the `Domilix` design (latent attention, post-norm
+         wiring) next to the `Megusun` design at equal size, and its kernels against their rooflines.
 N > 1: one process per GPU (torchrun), rows sharded across ranks, no data-path collective in the headline
          step; c5_splitkv is the mode with an exchange.
 """
@@ -65,6 +67,10 @@ def parse():
                     help="instead of the headline workload: prefill / decode throughput of the config-driven hybrid stack "
                          "(design Megusun) at realistic layer sizes next to CUDADecoder at equal size, and its kernels "
                          "against their rooflines (benchmarks/hybrid.py); one JSON line")
+    ap.add_argument("--latent", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the config-driven stack serving "
+                         "the Domilix design (latent attention) at realistic layer sizes next to the Megusun design at "
+                         "equal size, and its kernels against their rooflines (benchmarks/latent.py); one JSON line")
     return ap.parse_args()
 
 
@@ -442,6 +448,10 @@ def main():
     if args.hybrid:
         from benchmarks import hybrid
         print(json.dumps({"bench": "hybrid", **hybrid.run()}, default=float))
+        return
+    if args.latent:
+        from benchmarks import latent
+        print(json.dumps({"bench": "latent", **latent.run()}, default=float))
         return
     if args.impl == "reference":
         run_reference(args)

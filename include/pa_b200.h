@@ -672,7 +672,8 @@ int pa_moe_down(const void* d_act, const void* d_w_down, int ff, int width, int 
  *   kernel, any shape, both element types; nsplit > 1 cuts the keys of every tile into that many parts, workspace
  *   pa_latent_attention_workspace_bytes) or of at most pa_latent_attention_mma_tile_tokens(...) tokens (tile_kind 2:
  *   bfloat16 on the tensor cores; 0 = this shape is not served; PA_ERR_UNSUPPORTED where a shape or an alignment rules
- *   it out). */
+ *   it out).  tile_kind 3: tile_kind 2 with the promise that every tile holds ONE token (decoded tokens): with at most 16
+ *   heads the warps of the tensor-core kernel then split the keys of a step instead of the rows. */
 int pa_rope_table(const int32_t* d_row_pos, int rows, int dims, float base, float* d_table, pa_stream_t stream);
 int pa_rope_rows(void* d_x, int64_t stride, int off, int head_stride, int heads, int dims, const float* d_table,
                  int rows, int elem, pa_stream_t stream);

@@ -412,14 +412,19 @@ static int la_dispatch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
 // this precision.  KVR and ROT are the PADDED sizes: the real kv_rank / rot_dim values (multiples of 8) sit at the start
 // of their columns in shared memory, the rest is zero, and 16-wide steps that are all padding are skipped.  nsplit > 1
 // cuts the key steps into parts whose (m, l, acc) go to the float kernel's partial layout and merge kernel.
+// KSPLIT (decoded tokens of at most 16 heads: every tile is ONE token, so one 16-row group is all the rows there are):
+// the four warps of a column half SPLIT the 64 keys of a step, 16 each, over the same rows, and their (m, l, o) meet in
+// shared memory at the end -- a quarter of the MMAs per warp, which is what bounds a step that has so few rows.
 constexpr int kLmRows = 64, kLmKeys = 64, kLmThreads = 256, kLmPad = 8;
 
-template <int KVR, int ROT>
+template <int KVR, int ROT, bool KSPLIT>
 __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(const LatentAttnParams p) {
     constexpr int KD = KVR + ROT, KS = KD + kLmPad, NT = KVR / 16;     // NT 8-column tiles per warp (half of KVR)
+    constexpr int QR = KSPLIT ? 16 : kLmRows;                          // query rows staged
+    constexpr int NKG = KSPLIT ? 1 : 4;                                // groups of 16 keys a warp takes per step
     extern __shared__ __align__(16) unsigned char lm_smem[];
-    bf16_t* Qs = reinterpret_cast<bf16_t*>(lm_smem);                   // [64][KS]
-    bf16_t* Ks = Qs + kLmRows * KS;                                     // [2][64][KS]
+    bf16_t* Qs = reinterpret_cast<bf16_t*>(lm_smem);                   // [QR][KS]
+    bf16_t* Ks = Qs + QR * KS;                                          // [2][64][KS]
     __shared__ int key_ok[2][kLmKeys];
 
     int hc, nchunk;
@@ -430,6 +435,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     const int chunk = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp & 3, ch = warp >> 2;
+    const int kg0 = KSPLIT ? rg : 0, rbase = KSPLIT ? 0 : rg * 16;
     const int kv_rank = p.kv_rank, rot_dim = p.rot_dim, kd = kv_rank + rot_dim;
     const bf16_t* pool = static_cast<const bf16_t*>(p.pool);
     const int32_t* trow = p.table + (int64_t)slot * p.num_tiles;
@@ -439,7 +445,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     const int kt0 = blockIdx.z * per, kt1 = min(nkt, kt0 + per);
 
     // queries: piece v of a row is 8 columns of the latent part (v * 8 < KVR) or of the rotated part
-    for (int c = tid; c < kLmRows * (KD / 8); c += kLmThreads) {
+    for (int c = tid; c < QR * (KD / 8); c += kLmThreads) {
         const int r = c / (KD / 8), v = c % (KD / 8);
         const int tok = r / hc, hh = chunk * hc + r % hc;
         const bool row_ok = tok < bq && tok < ntok && hh < p.heads;
@@ -490,7 +496,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     bool any_row = false;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int r = rg * 16 + (lane >> 2) + 8 * i;
+        const int r = rbase + (lane >> 2) + 8 * i;
         const int tok = r / hc, hh = chunk * hc + r % hc;
         rpos[i] = (tok < bq && tok < ntok && hh < p.heads) ? pos0 + tok : -1;
         any_row |= rpos[i] >= 0;
@@ -505,29 +511,55 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
         cp_async_wait<1>();
         __syncthreads();
         if (active) {
-            float s[8][4];
+            float s[2 * NKG][4];
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
+            for (int t = 0; t < 2 * NKG; ++t)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) s[t][c] = 0.f;
+            // KSPLIT: a warp's two score tiles would be one chain of KD / 16 dependent MMAs each; four sets of
+            // accumulators taken in turn cut the chain to a quarter (summed below)
+            constexpr int NSET = KSPLIT ? 4 : 1;
+            float sx[NSET > 1 ? NSET - 1 : 1][2][4];
+            if (KSPLIT) {
+#pragma unroll
+                for (int e = 0; e < NSET - 1; ++e)
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) sx[e][t][c] = 0.f;
+            }
 #pragma unroll 4
             for (int ks = 0; ks < KD; ks += 16) {
                 if (ks < KVR ? ks >= kv_rank : ks - KVR >= rot_dim) continue;      // all padding
                 uint32_t a[4];
-                ldsm_x4(smem_u32(Qs + (rg * 16 + (lane & 15)) * KS + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+                ldsm_x4(smem_u32(Qs + (rbase + (lane & 15)) * KS + ks + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {
+                for (int np = 0; np < NKG; ++np) {
                     uint32_t b0, b1, b2, b3;
-                    ldsm_x4(smem_u32(Ks + (buf * kLmKeys + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + ks + ((lane >> 3) & 1) * 8),
+                    ldsm_x4(smem_u32(Ks + (buf * kLmKeys + (kg0 + np) * 16 + (lane & 7) + ((lane >> 4) << 3)) * KS + ks + ((lane >> 3) & 1) * 8),
                             b0, b1, b2, b3);
-                    mma_bf16_16816(s[2 * np], a, b0, b1);
-                    mma_bf16_16816(s[2 * np + 1], a, b2, b3);
+                    const int set = KSPLIT ? (ks / 16) % NSET : 0;
+                    if (KSPLIT && set > 0) {
+                        mma_bf16_16816(sx[set - 1][0], a, b0, b1);
+                        mma_bf16_16816(sx[set - 1][1], a, b2, b3);
+                    } else {
+                        mma_bf16_16816(s[2 * np], a, b0, b1);
+                        mma_bf16_16816(s[2 * np + 1], a, b2, b3);
+                    }
                 }
+            }
+            if (KSPLIT) {
+#pragma unroll
+                for (int e = 0; e < NSET - 1; ++e)
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) s[t][c] += sx[e][t][c];
             }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const int col = t * 8 + 2 * (lane & 3);
+            for (int t = 0; t < 2 * NKG; ++t) {
+                const int col = (2 * kg0 + t) * 8 + 2 * (lane & 3);
                 const int2 okk = *reinterpret_cast<const int2*>(&key_ok[buf][col]);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -554,14 +586,14 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
                 }
             }
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
+            for (int t = 0; t < 2 * NKG; ++t)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     s[t][c] = exp2f(s[t][c] - ref[c >> 1]);
                     l[c >> 1] += s[t][c];
                 }
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < NKG; ++kk) {
                 uint32_t a[4];
                 a[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
                 a[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
@@ -572,7 +604,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
                     const int col0 = ch * (KVR / 2) + np * 16;
                     if (col0 >= kv_rank) continue;               // all padding
                     uint32_t b0, b1, b2, b3;
-                    ldsm_x4_trans(smem_u32(Ks + (buf * kLmKeys + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + col0 + (lane >> 4) * 8),
+                    ldsm_x4_trans(smem_u32(Ks + (buf * kLmKeys + (kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + col0 + (lane >> 4) * 8),
                                   b0, b1, b2, b3);
                     mma_bf16_16816(o[2 * np], a, b0, b1);
                     mma_bf16_16816(o[2 * np + 1], a, b2, b3);
@@ -582,6 +614,56 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
         __syncthreads();                                         // this buffer is free for the copies of step kt + 2
     }
     cp_async_wait<0>();
+    bool fin = true;                                             // this warp finishes rows
+    if (KSPLIT) {
+        // [rg][ch][lane][m0 m1 l0 l1 o...] over the key buffers (odd stride: conflict-free); warp rg == 0 of each column
+        // half merges the four parts into its registers
+        constexpr int PST = 4 + NT * 4 + 1;
+        float* Pm = reinterpret_cast<float*>(Ks);
+        float* mine = Pm + ((rg * 2 + ch) * 32 + lane) * PST;
+        mine[0] = m[0]; mine[1] = m[1]; mine[2] = l[0]; mine[3] = l[1];
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mine[4 + t * 4 + c] = o[t][c];
+        __syncthreads();
+        fin = rg == 0;
+        if (fin) {
+            float M[2] = {m[0], m[1]};
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+                const float* pq = Pm + ((q * 2 + ch) * 32 + lane) * PST;
+                M[0] = fmaxf(M[0], pq[0]);
+                M[1] = fmaxf(M[1], pq[1]);
+            }
+            float w0[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                w0[i] = m[i] == -INFINITY ? 0.f : exp2f(m[i] - M[i]);
+                l[i] *= w0[i];
+                m[i] = M[i];
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[t][c] *= w0[c >> 1];
+#pragma unroll
+            for (int q = 1; q < 4; ++q) {
+                const float* pq = Pm + ((q * 2 + ch) * 32 + lane) * PST;
+                float wq[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    wq[i] = pq[i] == -INFINITY ? 0.f : exp2f(pq[i] - M[i]);
+                    l[i] = fmaf(wq[i], pq[2 + i], l[i]);
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) o[t][c] = fmaf(wq[c >> 1], pq[4 + t * 4 + c], o[t][c]);
+            }
+        }
+    }
+    if (!fin) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
@@ -589,7 +671,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int r = rg * 16 + (lane >> 2) + 8 * i;
+        const int r = rbase + (lane >> 2) + 8 * i;
         if (rpos[i] < 0) continue;
         const int tok = r / hc, hh = chunk * hc + r % hc;
         if (p.nsplit > 1) {
@@ -619,11 +701,11 @@ static int lm_merge(const LatentAttnParams& p, int ntiles, int nchunk, cudaStrea
     PA_RETURN_LAUNCH_STATUS();
 }
 
-template <int KVR, int ROT>
-static int lm_launch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
-    const size_t smem = (size_t)3 * kLmRows * (KVR + ROT + kLmPad) * sizeof(bf16_t);
+template <int KVR, int ROT, bool KSPLIT>
+static int lm_launch_as(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
+    const size_t smem = (size_t)((KSPLIT ? 16 : kLmRows) + 2 * kLmKeys) * (KVR + ROT + kLmPad) * sizeof(bf16_t);
     if (smem > (size_t)device_info().max_smem_optin) return PA_ERR_UNSUPPORTED;
-    auto kern = latent_attention_mma_kernel<KVR, ROT>;
+    auto kern = latent_attention_mma_kernel<KVR, ROT, KSPLIT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int hc, nchunk;
@@ -640,19 +722,25 @@ static int lm_launch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
     PA_RETURN_LAUNCH_STATUS();
 }
 
+template <int KVR, int ROT>
+static int lm_launch(const LatentAttnParams& p, int ntiles, bool one_token_tiles, cudaStream_t st) {
+    if (one_token_tiles && p.heads <= 16) return lm_launch_as<KVR, ROT, true>(p, ntiles, st);
+    return lm_launch_as<KVR, ROT, false>(p, ntiles, st);
+}
+
 static bool lm_shape_ok(int kv_rank, int rot_dim) {
     return kv_rank % 8 == 0 && kv_rank >= 8 && kv_rank <= 512 && rot_dim % 8 == 0 && rot_dim <= 64;
 }
 
 // PA_ERR_UNSUPPORTED: this shape or these pointers stay on the float kernel
-static int lm_dispatch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
+static int lm_dispatch(const LatentAttnParams& p, int ntiles, bool one_token_tiles, cudaStream_t st) {
     if (!lm_shape_ok(p.kv_rank, p.rot_dim)) return PA_ERR_UNSUPPORTED;
     if (p.ql_rs % 8 || p.ql_hs % 8 || p.o_rs % 2 || p.o_hs % 2) return PA_ERR_UNSUPPORTED;
     if (p.rot_dim && (p.qr_rs % 8 || p.qr_hs % 8 || (uintptr_t)p.q_rot % 16)) return PA_ERR_UNSUPPORTED;
     if ((uintptr_t)p.q_lat % 16 || (uintptr_t)p.pool % 16 || (uintptr_t)p.out % 4) return PA_ERR_UNSUPPORTED;
     const int kp = p.kv_rank <= 64 ? 64 : p.kv_rank <= 128 ? 128 : p.kv_rank <= 256 ? 256 : 512;
     const int rp = p.rot_dim <= 32 ? 32 : 64;
-#define PA_LM_CASE(K, R) if (kp == K && rp == R) return lm_launch<K, R>(p, ntiles, st)
+#define PA_LM_CASE(K, R) if (kp == K && rp == R) return lm_launch<K, R>(p, ntiles, one_token_tiles, st)
     PA_LM_CASE(64, 32); PA_LM_CASE(64, 64); PA_LM_CASE(128, 32); PA_LM_CASE(128, 64);
     PA_LM_CASE(256, 32); PA_LM_CASE(256, 64); PA_LM_CASE(512, 32); PA_LM_CASE(512, 64);
 #undef PA_LM_CASE
@@ -769,9 +857,10 @@ PA_API int pa_latent_attention(const void* d_q_lat, int64_t ql_row_stride, int64
     p.pool = d_pool; p.table = d_table; p.num_slots = num_slots; p.num_tiles = num_tiles; p.total_pages = total_pages;
     p.tile_size = tile_size; p.tiles = d_q_tiles; p.heads = heads; p.kv_rank = kv_rank; p.rot_dim = rot_dim; p.scale = scale;
     p.out = d_out; p.o_rs = o_row_stride; p.o_hs = o_head_stride; p.nsplit = nsplit; p.partial = static_cast<float*>(d_workspace);
-    p.cta_rows = tile_kind == 2 ? kLmRows : kLaRows;
+    p.cta_rows = tile_kind >= 2 ? kLmRows : kLaRows;
     if (elem != 4 && elem != 2) return PA_ERR_UNSUPPORTED;
-    if (tile_kind == 2) return elem == 2 ? lm_dispatch(p, num_q_tiles, as_stream(stream)) : PA_ERR_UNSUPPORTED;
+    if (tile_kind == 2 || tile_kind == 3)
+        return elem == 2 ? lm_dispatch(p, num_q_tiles, tile_kind == 3, as_stream(stream)) : PA_ERR_UNSUPPORTED;
     if (tile_kind != 0) return PA_ERR_UNSUPPORTED;
     if (elem == 4) return la_dispatch<float>(p, num_q_tiles, as_stream(stream));
     return la_dispatch<bf16_t>(p, num_q_tiles, as_stream(stream));

@@ -182,6 +182,14 @@ class DiffAttentionMixer:
         return c.model._linear(out, self.w_o)
 
 
+def latent_key_splits(ctas, longest, sms):
+    """Too few CTAs for the chip over a long context: cut the keys into parts (at least 256 keys each), as many as still
+    make ONE wave of CTAs -- the kernels hold most of an SM's shared memory, so a second, partial wave costs a whole one."""
+    if ctas >= sms or longest <= 512:
+        return 1
+    return max(1, min(sms // ctas, longest // 256, 64))
+
+
 class LatentAttentionMixer:
     """Attention through a low-rank latent over a paged pool with ONE row per token (KVTileCache with one key/value head
     and no value pool: row = [c | kr]).  The per-head key and value maps are applied on the query side and after the
@@ -268,20 +276,19 @@ class LatentAttentionMixer:
         sms = c.model.sm_count
         mma = self.mma_tokens > 0
         rows_per_cta = 64 if mma else 32
-        for _kind, group in b.query_tiles(self.mma_tokens if mma else self.tile_tokens).items():
+        for kind, group in b.query_tiles(self.mma_tokens if mma else self.tile_tokens).items():
             if group is None:
                 continue
             tiles, ntiles, longest = group
-            nsplit, ws = 1, None
-            ctas = ntiles * math.ceil(H / rows_per_cta)
-            if ctas < 2 * sms and longest > 512:          # too few CTAs for the chip over a long context: cut the keys
-                nsplit = max(1, min(math.ceil(2 * sms / ctas), longest // 256, 64))
+            ws = None
+            nsplit = latent_key_splits(ntiles * math.ceil(H / rows_per_cta), longest, sms)
             if nsplit > 1:
                 ws = c.empty(lib.pa_latent_attention_workspace_bytes(ntiles, H, kvr, nsplit), dtype=torch.uint8)
             _chk(lib.pa_latent_attention(ql.data_ptr(), kvr, R * kvr, q.data_ptr() + self.dim * c.elem, q.stride(0), self.qd,
                                          kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_tiles_,
                                          kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, H, kvr, self.rot_dim,
-                                         self.scale, lat.data_ptr(), kvr, R * kvr, c.elem, nsplit, 2 if mma else 0,
+                                         self.scale, lat.data_ptr(), kvr, R * kvr, c.elem, nsplit,
+                                         (3 if kind == 1 else 2) if mma else 0,
                                          _cabi.ptr(ws), ws.numel() if ws is not None else 0, s), "pa_latent_attention")
         ov = self._head_linear(c, lat, kvr, R * kvr, self.w_uv, kvr, self.vdim)               # [H, R, vdim]
         og = c.empty(R, H * self.vdim)

@@ -601,11 +601,12 @@ def test_latent_attention_kernels_alone(heads, kv_rank, rot_dim, tile_size):
     ql = torch.randn(R_, heads, kv_rank, generator=g) * 0.3
     qr = torch.randn(R_, heads, max(rot_dim, 1), generator=g) * 0.3
     scale = 0.35
-    for elem, kind in ((4, 0), (2, 0), (2, 2)):
+    for elem, kind in ((4, 0), (2, 0), (2, 2), (2, 3)):
         dt = torch.float32 if elem == 4 else torch.bfloat16
-        if kind == 2 and not lib.pa_latent_attention_mma_tile_tokens(heads, kv_rank, rot_dim, elem):
+        if kind >= 2 and not lib.pa_latent_attention_mma_tile_tokens(heads, kv_rank, rot_dim, elem):
             continue
         tt = lib.pa_latent_attention_mma_tile_tokens(heads, kv_rank, rot_dim, elem) if kind == 2 else lib.pa_latent_attention_tile_tokens(heads)
+        tt = 1 if kind == 3 else tt                 # kind 3 promises tiles of one token (its key-split form: at most 16 heads)
         poold, qld, qrd, tabled = pool.to(dt).to(dev), ql.to(dt).to(dev), qr.to(dt).to(dev), table.to(dev)
         P, QL, QR = poold.cpu().double(), qld.cpu().double(), qrd.cpu().double()
         want = torch.zeros(R_, heads, kv_rank, dtype=torch.float64)
