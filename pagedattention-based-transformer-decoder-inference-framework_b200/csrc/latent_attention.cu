@@ -175,6 +175,21 @@ __global__ void head_gate_kernel(const T* __restrict__ in, int64_t i_rs, int64_t
     out[i] = from_f32<T>(to_f32<T>(in[r * i_rs + (int64_t)h * i_hs + v]) * g);
 }
 
+// the same on bfloat16 rows with 16-byte aligned head vectors: eight outputs per thread
+__global__ void head_gate_bf16x8_kernel(const bf16_t* __restrict__ in, int64_t i_rs, int64_t i_hs, const bf16_t* __restrict__ gate,
+                                        int64_t g_rs, int heads, int vdim, int64_t rows, bf16_t* __restrict__ out) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= rows * heads * vdim) return;
+    const int v = (int)(i % vdim), h = (int)((i / vdim) % heads);
+    const int64_t r = i / ((int64_t)vdim * heads);
+    const float g = sigmoid_f32(__bfloat162float(gate[r * g_rs + h]));
+    float f[8];
+    bf16x8_unpack(*reinterpret_cast<const uint4*>(in + r * i_rs + (int64_t)h * i_hs + v), f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] *= g;
+    *reinterpret_cast<uint4*>(out + i) = bf16x8_pack(f);
+}
+
 // ---- attention: float tile kernel -----------------------------------------------------------------------------------
 constexpr int kLaRows = 32;     // (token, head) rows per CTA
 constexpr int kLaWarps = 8;
@@ -815,6 +830,13 @@ PA_API int pa_head_gate(const void* d_in, int64_t in_row_stride, int64_t in_head
     PA_CHECK_ARG(d_in && d_gate && d_out && heads > 0 && vdim > 0 && rows >= 0);
     const int64_t n = rows * heads * vdim;
     if (n == 0) return PA_OK;
+    if (elem == 2 && vdim % 8 == 0 && in_row_stride % 8 == 0 && in_head_stride % 8 == 0 && (uintptr_t)d_in % 16 == 0 &&
+        (uintptr_t)d_out % 16 == 0) {
+        head_gate_bf16x8_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, as_stream(stream)>>>(
+            static_cast<const bf16_t*>(d_in), in_row_stride, in_head_stride, static_cast<const bf16_t*>(d_gate), gate_row_stride,
+            heads, vdim, rows, static_cast<bf16_t*>(d_out));
+        PA_RETURN_LAUNCH_STATUS();
+    }
     PA_DISPATCH_ELEM(elem, head_gate_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
                                static_cast<const T*>(d_in), in_row_stride, in_head_stride, static_cast<const T*>(d_gate),
                                gate_row_stride, heads, vdim, rows, static_cast<T*>(d_out)));

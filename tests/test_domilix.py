@@ -562,16 +562,18 @@ def test_plain_experts_with_squared_relu(rows, experts, top, width, ff, elem):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("elem", [4, 2])
-def test_gated_relu_product_kernel(elem):
+@pytest.mark.parametrize("ff", [19, 24])
+def test_gated_relu_product_kernel(elem, ff):
+    """ff = 24: the bfloat16 form that takes eight values per thread; 19: the element-wise one."""
     cabi, lib, dev, s = _lib()
     dt = torch.bfloat16 if elem == 2 else torch.float32
-    gu = torch.randn(37, 2 * 19, generator=torch.Generator().manual_seed(2)).to(dt)
-    out = torch.empty(37, 19, dtype=dt, device=dev)
+    gu = torch.randn(37, 2 * ff, generator=torch.Generator().manual_seed(2)).to(dt)
+    out = torch.empty(37, ff, dtype=dt, device=dev)
     for act, fn in ((1, torch.relu), (0, torch.nn.functional.silu),
                     (2, lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))))):
         gud = gu.to(dev)
-        cabi.check(lib.pa_act_mul(gud.data_ptr(), 37, 19, act, out.data_ptr(), elem, s()), "act_mul")
-        want = fn(gu.double()[:, :19]) * gu.double()[:, 19:]
+        cabi.check(lib.pa_act_mul(gud.data_ptr(), 37, ff, act, out.data_ptr(), elem, s()), "act_mul")
+        want = fn(gu.double()[:, :ff]) * gu.double()[:, ff:]
         assert (out.cpu().double() - want).abs().max() < (1e-5 if elem == 4 else 3e-2)
 
 
