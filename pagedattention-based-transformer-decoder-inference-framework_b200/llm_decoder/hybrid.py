@@ -252,6 +252,33 @@ class LatentAttentionMixer:
                                   _cabi.stream()), "pa_head_linear")
         return out
 
+    def _attend(self, c, q, ql, lat, mma):
+        """Launch the attention kernels over this step's tiles (prompt portions, then single decoded tokens).  Returns
+        False when the tensor-core kernel refuses the operands (nothing was written that the float kernel does not
+        write again)."""
+        b, lib, kv, s, R, H, kvr = c.batch, c.lib, self.kv, _cabi.stream(), c.R, self.heads, self.kv_rank
+        pt = kv.page_table_
+        table = pt.device_data()
+        rows_per_cta = 64 if mma else 32
+        for kind, group in b.query_tiles(self.mma_tokens if mma else self.tile_tokens).items():
+            if group is None:
+                continue
+            tiles, ntiles, longest = group
+            ws = None
+            nsplit = latent_key_splits(ntiles * math.ceil(H / rows_per_cta), longest, c.model.sm_count)
+            if nsplit > 1:
+                ws = c.empty(lib.pa_latent_attention_workspace_bytes(ntiles, H, kvr, nsplit), dtype=torch.uint8)
+            st = lib.pa_latent_attention(ql.data_ptr(), kvr, R * kvr, q.data_ptr() + self.dim * c.elem, q.stride(0), self.qd,
+                                         kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_tiles_,
+                                         kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, H, kvr, self.rot_dim,
+                                         self.scale, lat.data_ptr(), kvr, R * kvr, c.elem, nsplit,
+                                         (3 if kind == 1 else 2) if mma else 0, _cabi.ptr(ws),
+                                         ws.numel() if ws is not None else 0, s)
+            if mma and st == _cabi.PA_ERR_UNSUPPORTED:
+                return False
+            _chk(st, "pa_latent_attention")
+        return True
+
     def forward(self, c, h):
         b, lib, kv, s, R, H = c.batch, c.lib, self.kv, _cabi.stream(), c.R, self.heads
         proj = c.model._linear(h, self.w_in)
@@ -273,23 +300,10 @@ class LatentAttentionMixer:
         kvr = self.kv_rank
         ql = self._head_linear(c, q, q.stride(0), self.qd, self.w_uk, self.dim, kvr)          # [H, R, kv_rank]
         lat = c.empty(H, R, kvr)
-        sms = c.model.sm_count
-        mma = self.mma_tokens > 0
-        rows_per_cta = 64 if mma else 32
-        for kind, group in b.query_tiles(self.mma_tokens if mma else self.tile_tokens).items():
-            if group is None:
-                continue
-            tiles, ntiles, longest = group
-            ws = None
-            nsplit = latent_key_splits(ntiles * math.ceil(H / rows_per_cta), longest, sms)
-            if nsplit > 1:
-                ws = c.empty(lib.pa_latent_attention_workspace_bytes(ntiles, H, kvr, nsplit), dtype=torch.uint8)
-            _chk(lib.pa_latent_attention(ql.data_ptr(), kvr, R * kvr, q.data_ptr() + self.dim * c.elem, q.stride(0), self.qd,
-                                         kv.key_buffer_.data_ptr(), table.data_ptr(), pt.num_beams_, pt.num_tiles_,
-                                         kv.total_pages_, kv.tile_size_, tiles.data_ptr(), ntiles, H, kvr, self.rot_dim,
-                                         self.scale, lat.data_ptr(), kvr, R * kvr, c.elem, nsplit,
-                                         (3 if kind == 1 else 2) if mma else 0,
-                                         _cabi.ptr(ws), ws.numel() if ws is not None else 0, s), "pa_latent_attention")
+        if self.mma_tokens > 0 and not self._attend(c, q, ql, lat, True):
+            self.mma_tokens = 0         # a stride or an alignment the tensor-core kernel does not take: the float kernel
+        if self.mma_tokens == 0:
+            self._attend(c, q, ql, lat, False)
         ov = self._head_linear(c, lat, kvr, R * kvr, self.w_uv, kvr, self.vdim)               # [H, R, vdim]
         og = c.empty(R, H * self.vdim)
         _chk(lib.pa_head_gate(ov.data_ptr(), self.vdim, R * self.vdim, proj.data_ptr() + self.g_off * c.elem, proj.stride(0),
