@@ -369,6 +369,72 @@ def test_greedy_generation_through_the_scheduler(dtype):
             #                                                         bfloat16 logits, each off by up to ~0.15 here
 
 
+def _random_config(rnd):
+    """Layer count, order, which layers borrow which pool, every size and constant drawn at random."""
+    layers, owners, shapes = [], [], {}
+    for i in range(rnd.randint(2, 6)):
+        mlp = rnd.choice([None, "dense", "moe", "moe"])
+        if mlp == "dense":
+            mlp = R.dense_mlp(rnd.choice([24, 64, 100, 37]))
+        elif mlp == "moe":
+            experts = rnd.randint(2, 12)
+            mlp = R.moe_mlp(experts, rnd.randint(1, experts), rnd.choice([8, 16, 24, 30]))
+        own = dict(heads=rnd.randint(1, 9), dim=rnd.choice([8, 16, 24, 12]), vdim=rnd.choice([8, 16, 40, 20]), q_rank=rnd.choice([16, 24, 48, 30]))
+        if owners and rnd.random() < 0.5:
+            j = rnd.choice(owners)
+            layers.append(R.latent_layer(**{**shapes[j], **own}, kv_from=j, mlp=mlp, scale=rnd.uniform(0.1, 0.4)))
+        else:
+            shapes[i] = dict(own, rot_dim=rnd.choice([2, 4, 8, 16, 24]), kv_rank=rnd.choice([16, 24, 48, 64, 72, 136, 30]),
+                             base=rnd.choice([50.0, 1000.0, 20000.0]))
+            owners.append(i)
+            layers.append(R.latent_layer(**shapes[i], mlp=mlp, scale=rnd.uniform(0.1, 0.4)))
+    return R.make_config(layers, width=rnd.choice([40, 64, 72, 96, 50, 128, 200]), vocab=rnd.choice([61, 97, 128]),
+                         eps=rnd.choice([1e-5, 1e-6]), embed_scale=rnd.uniform(0.5, 3.0))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(6))
+def test_random_configurations_in_random_schedules(seed):
+    """Three requests of a randomly drawn model advance in random portions (1 to 100 tokens, some sitting out) through
+    one engine; float32 against the oracle at every position, bfloat16 finite and equal to its own whole-prompt run up
+    to rounding."""
+    import llm_decoder as ld
+    rnd = random.Random(seed)
+    config = _random_config(rnd)
+    W = R.random_weights(config, seed)
+    reqs = {r: _tokens(n, config["vocab"], 100 * seed + i)
+            for i, (r, n) in enumerate((("a", rnd.randint(120, 300)), ("b", rnd.randint(2, 90)), ("c", rnd.randint(1, 40))))}
+    plan, at = [], {r: 0 for r in reqs}
+    while any(at[r] < len(reqs[r]) for r in reqs):
+        step = []
+        for r in reqs:
+            left = len(reqs[r]) - at[r]
+            if left and rnd.random() < 0.8:
+                n = min(left, rnd.choice([1, 1, 2, 3, 17, 64, 100]))
+                step.append((r, at[r], n))
+                at[r] += n
+        if step:
+            plan.append(step)
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = ld.Engine(_model(config, W, dtype, max_tokens=640, max_seqs=3))
+        got = {r: [] for r in reqs}
+        for step in plan:
+            out = eng.step([(r, reqs[r][lo:lo + n], list(range(n))) for r, lo, n in step])
+            o = 0
+            for r, _lo, n in step:
+                got[r].append(out[o:o + n])
+                o += n
+        outs[dtype] = {r: torch.cat(got[r]) for r in reqs}
+    for r in reqs:
+        _close(outs["float32"][r], R.forward(config, W, reqs[r])[0])
+        whole = ld.Engine(_model(config, W, "bfloat16", max_tokens=640, max_seqs=3)).step([(r, reqs[r], list(range(len(reqs[r]))))])
+        b16 = outs["bfloat16"][r].double().cpu()
+        assert torch.isfinite(b16).all()
+        rel = (b16 - whole.double().cpu()).pow(2).mean(-1).sqrt() / whole.double().cpu().pow(2).mean(-1).sqrt()
+        assert rel.sort().values[int(0.8 * (rel.numel() - 1))].item() < BF16_TOL
+
+
 @pytest.mark.gpu
 def test_trace_runner_and_generate_cli(tmp_path):
     """bin/trace_run and bin/generate on a model folder: registry -> engine -> files."""
