@@ -432,7 +432,8 @@ static int la_dispatch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
 // shared memory at the end -- a quarter of the MMAs per warp, which is what bounds a step that has so few rows.
 constexpr int kLmRows = 64, kLmKeys = 64, kLmThreads = 256, kLmPad = 8;
 
-template <int KVR, int ROT, bool KSPLIT>
+// EXACT: kv_rank == KVR and rot_dim == ROT, so no column is padding and the checks for it fold away.
+template <int KVR, int ROT, bool KSPLIT, bool EXACT>
 __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(const LatentAttnParams p) {
     constexpr int KD = KVR + ROT, KS = KD + kLmPad, NT = KVR / 16;     // NT 8-column tiles per warp (half of KVR)
     constexpr int QR = KSPLIT ? 16 : kLmRows;                          // query rows staged
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp & 3, ch = warp >> 2;
     const int kg0 = KSPLIT ? rg : 0, rbase = KSPLIT ? 0 : rg * 16;
-    const int kv_rank = p.kv_rank, rot_dim = p.rot_dim, kd = kv_rank + rot_dim;
+    const int kv_rank = EXACT ? KVR : p.kv_rank, rot_dim = EXACT ? ROT : p.rot_dim, kd = kv_rank + rot_dim;
     const bf16_t* pool = static_cast<const bf16_t*>(p.pool);
     const int32_t* trow = p.table + (int64_t)slot * p.num_tiles;
     const int total = pos0 + ntok;
@@ -483,10 +484,11 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
         }
         return -1;
     };
-    // four threads per key: one page look-up per thread and step; a thread copies every fourth 16-byte piece of its row
-    auto load_tile = [&](int kt, int buf) {
-        const int key = tid >> 2, q4 = tid & 3;
-        const int64_t pr = pool_row(kt * kLmKeys + key);
+    // four threads per key: one page look-up per thread and step, made one step before its copies are issued (the
+    // look-up's latency would otherwise sit in front of every step's copies); a thread copies every fourth 16-byte piece
+    // of its row
+    const int key = tid >> 2, q4 = tid & 3;
+    auto load_tile = [&](int64_t pr, int buf) {
         if (q4 == 0) key_ok[buf][key] = pr >= 0;
         bf16_t* dst = Ks + (buf * kLmKeys + key) * KS;
         const bf16_t* src = pool + (pr >= 0 ? pr * kd : 0);
@@ -498,8 +500,9 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
             cp_async_16(smem_u32(dst + col), ok ? src + (lat ? col : kv_rank + col - KVR) : pool, ok);
         }
     };
-    if (kt0 < kt1) load_tile(kt0, 0);
+    if (kt0 < kt1) load_tile(pool_row(kt0 * kLmKeys + key), 0);
     cp_async_commit();
+    int64_t pr_next = kt0 + 1 < kt1 ? pool_row((kt0 + 1) * kLmKeys + key) : -1;
 
     float o[NT][4];
 #pragma unroll
@@ -521,8 +524,9 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
 
     for (int kt = kt0; kt < kt1; ++kt) {
         const int buf = (kt - kt0) & 1, c0 = kt * kLmKeys;
-        if (kt + 1 < kt1) load_tile(kt + 1, buf ^ 1);
+        if (kt + 1 < kt1) load_tile(pr_next, buf ^ 1);
         cp_async_commit();
+        pr_next = kt + 2 < kt1 ? pool_row((kt + 2) * kLmKeys + key) : -1;
         cp_async_wait<1>();
         __syncthreads();
         if (active) {
@@ -720,7 +724,8 @@ template <int KVR, int ROT, bool KSPLIT>
 static int lm_launch_as(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
     const size_t smem = (size_t)((KSPLIT ? 16 : kLmRows) + 2 * kLmKeys) * (KVR + ROT + kLmPad) * sizeof(bf16_t);
     if (smem > (size_t)device_info().max_smem_optin) return PA_ERR_UNSUPPORTED;
-    auto kern = latent_attention_mma_kernel<KVR, ROT, KSPLIT>;
+    const bool exact = p.kv_rank == KVR && p.rot_dim == ROT;
+    auto kern = exact ? latent_attention_mma_kernel<KVR, ROT, KSPLIT, true> : latent_attention_mma_kernel<KVR, ROT, KSPLIT, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int hc, nchunk;
