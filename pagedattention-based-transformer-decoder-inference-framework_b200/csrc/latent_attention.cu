@@ -420,9 +420,12 @@ static int la_dispatch(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
 // columns of half (w >> 2) of the output, so the accumulators of a 512-wide latent are 128 registers per thread.  Per
 // step 64 keys are located through the page table and brought in with 16-byte cp.async copies into one of two buffers
 // (the copies of step t + 1 fly while step t is multiplied); the staged rows serve both products: S = Q K^T over all
-// kv_rank + rot_dim columns (mma.sync m16n8k16, bfloat16 operands, float accumulators; both warps of a row group compute
-// the scores of their 16 rows, which costs less than handing the weights across), and O += P V with V = the first
-// kv_rank columns of the same rows, read transposed by ldmatrix.  Scores, the running maximum, the exponentials and
+// kv_rank + rot_dim columns (mma.sync m16n8k16, bfloat16 operands, float accumulators) and O += P V with V = the first
+// kv_rank columns of the same rows, read transposed by ldmatrix.  The two warps of a row group SPLIT the 64 keys of a
+// step for the scores (32 each): they exchange their row maxima and then their halves of P (bfloat16, the operand
+// type of the second product anyway) through shared memory behind 64-thread named barriers, so no score is computed
+// twice; each keeps the sum of its own half and the two sums meet at the end.  A key's validity flag lives in the
+// padding of its staged row.  Scores, the running maximum, the exponentials and
 // their sum are float; the weights enter the second product rounded to bfloat16, like every other matrix operand of
 // this precision.  KVR and ROT are the PADDED sizes: the real kv_rank / rot_dim values (multiples of 8) sit at the start
 // of their columns in shared memory, the rest is zero, and 16-wide steps that are all padding are skipped.  nsplit > 1
@@ -437,11 +440,11 @@ template <int KVR, int ROT, bool KSPLIT, bool EXACT>
 __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(const LatentAttnParams p) {
     constexpr int KD = KVR + ROT, KS = KD + kLmPad, NT = KVR / 16;     // NT 8-column tiles per warp (half of KVR)
     constexpr int QR = KSPLIT ? 16 : kLmRows;                          // query rows staged
-    constexpr int NKG = KSPLIT ? 1 : 4;                                // groups of 16 keys a warp takes per step
+    constexpr int NKG = KSPLIT ? 1 : 2;                                // groups of 16 keys a warp scores per step
     extern __shared__ __align__(16) unsigned char lm_smem[];
     bf16_t* Qs = reinterpret_cast<bf16_t*>(lm_smem);                   // [QR][KS]
-    bf16_t* Ks = Qs + QR * KS;                                          // [2][64][KS]
-    __shared__ int key_ok[2][kLmKeys];
+    bf16_t* Ks = Qs + QR * KS;                                          // [2][64][KS]; column KD of a row: the key is mapped
+    bf16_t* Ps = Ks + 2 * kLmKeys * KS;                                 // !KSPLIT: [4 row groups][16][64] weights
 
     int hc, nchunk;
     la_geometry(p.heads, kLmRows, hc, nchunk);
@@ -451,7 +454,10 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     const int chunk = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = warp & 3, ch = warp >> 2;
-    const int kg0 = KSPLIT ? rg : 0, rbase = KSPLIT ? 0 : rg * 16;
+    const int kg0 = KSPLIT ? rg : 2 * ch, rbase = KSPLIT ? 0 : rg * 16;
+    bf16_t* Pp = Ps + rg * 16 * kLmKeys;                                // this row group's weights (and its mailbox)
+    float* Mb = reinterpret_cast<float*>(Pp);                           // [2 column halves][16 rows], between barriers
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + rg) : "memory"); };
     const int kv_rank = EXACT ? KVR : p.kv_rank, rot_dim = EXACT ? ROT : p.rot_dim, kd = kv_rank + rot_dim;
     const bf16_t* pool = static_cast<const bf16_t*>(p.pool);
     const int32_t* trow = p.table + (int64_t)slot * p.num_tiles;
@@ -489,7 +495,7 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
     // of its row
     const int key = tid >> 2, q4 = tid & 3;
     auto load_tile = [&](int64_t pr, int buf) {
-        if (q4 == 0) key_ok[buf][key] = pr >= 0;
+        if (q4 == 0) reinterpret_cast<uint16_t*>(Ks + (buf * kLmKeys + key) * KS)[KD] = pr >= 0;
         bf16_t* dst = Ks + (buf * kLmKeys + key) * KS;
         const bf16_t* src = pool + (pr >= 0 ? pr * kd : 0);
 #pragma unroll
@@ -579,11 +585,12 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
 #pragma unroll
             for (int t = 0; t < 2 * NKG; ++t) {
                 const int col = (2 * kg0 + t) * 8 + 2 * (lane & 3);
-                const int2 okk = *reinterpret_cast<const int2*>(&key_ok[buf][col]);
+                const uint16_t* kok = reinterpret_cast<const uint16_t*>(Ks + (buf * kLmKeys + col) * KS) + KD;
+                const int ok0 = kok[0], ok1 = kok[KS];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int i = c >> 1;
-                    const bool vis = ((c & 1) ? okk.y : okk.x) && c0 + col + (c & 1) <= rpos[i];
+                    const bool vis = ((c & 1) ? ok1 : ok0) && c0 + col + (c & 1) <= rpos[i];
                     s[t][c] = vis ? s[t][c] * sc : -INFINITY;
                     mx[i] = fmaxf(mx[i], s[t][c]);
                 }
@@ -593,6 +600,19 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
             for (int i = 0; i < 2; ++i) {
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            }
+            if (!KSPLIT) {                                       // the row maximum over the partner's 32 keys too
+                if ((lane & 3) == 0) {
+                    Mb[ch * 16 + (lane >> 2)] = mx[0];
+                    Mb[ch * 16 + (lane >> 2) + 8] = mx[1];
+                }
+                pair_sync();
+                mx[0] = fmaxf(mx[0], Mb[(ch ^ 1) * 16 + (lane >> 2)]);
+                mx[1] = fmaxf(mx[1], Mb[(ch ^ 1) * 16 + (lane >> 2) + 8]);
+                pair_sync();                                     // both have read: the weights may overwrite the mailbox
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
                 const float mn = fmaxf(m[i], mx[i]);
                 ref[i] = mn == -INFINITY ? 0.f : mn;
                 const float corr = exp2f(m[i] - ref[i]);         // m = -inf: 0 (nothing accumulated yet)
@@ -611,19 +631,34 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
                     s[t][c] = exp2f(s[t][c] - ref[c >> 1]);
                     l[c >> 1] += s[t][c];
                 }
+            if (!KSPLIT) {                                       // this warp's half of the weights -> shared memory
 #pragma unroll
-            for (int kk = 0; kk < NKG; ++kk) {
+                for (int t = 0; t < 2 * NKG; ++t) {
+                    bf16_t* dst = Pp + (lane >> 2) * kLmKeys + (2 * kg0 + t) * 8 + 2 * (lane & 3);
+                    *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(s[t][0], s[t][1]);
+                    *reinterpret_cast<uint32_t*>(dst + 8 * kLmKeys) = pack_bf16x2(s[t][2], s[t][3]);
+                }
+                pair_sync();
+            }
+            constexpr int NPV = KSPLIT ? 1 : 4;                  // groups of 16 keys in the second product
+#pragma unroll
+            for (int kk = 0; kk < NPV; ++kk) {
                 uint32_t a[4];
-                a[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
-                a[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
-                a[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                a[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                if (KSPLIT) {
+                    a[0] = pack_bf16x2(s[0][0], s[0][1]);
+                    a[1] = pack_bf16x2(s[0][2], s[0][3]);
+                    a[2] = pack_bf16x2(s[1][0], s[1][1]);
+                    a[3] = pack_bf16x2(s[1][2], s[1][3]);
+                } else {
+                    ldsm_x4(smem_u32(Pp + (lane & 15) * kLmKeys + kk * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+                }
+                const int kg = KSPLIT ? kg0 : kk;
 #pragma unroll
                 for (int np = 0; np < NT / 2; ++np) {
                     const int col0 = ch * (KVR / 2) + np * 16;
                     if (col0 >= kv_rank) continue;               // all padding
                     uint32_t b0, b1, b2, b3;
-                    ldsm_x4_trans(smem_u32(Ks + (buf * kLmKeys + (kg0 + kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + col0 + (lane >> 4) * 8),
+                    ldsm_x4_trans(smem_u32(Ks + (buf * kLmKeys + kg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + col0 + (lane >> 4) * 8),
                                   b0, b1, b2, b3);
                     mma_bf16_16816(o[2 * np], a, b0, b1);
                     mma_bf16_16816(o[2 * np + 1], a, b2, b3);
@@ -688,6 +723,15 @@ __global__ void __launch_bounds__(kLmThreads, 1) latent_attention_mma_kernel(con
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     }
+    if (!KSPLIT && active) {                                     // the sum over the partner's keys
+        if ((lane & 3) == 0) {
+            Mb[ch * 16 + (lane >> 2)] = l[0];
+            Mb[ch * 16 + (lane >> 2) + 8] = l[1];
+        }
+        pair_sync();
+        l[0] += Mb[(ch ^ 1) * 16 + (lane >> 2)];
+        l[1] += Mb[(ch ^ 1) * 16 + (lane >> 2) + 8];
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = rbase + (lane >> 2) + 8 * i;
@@ -722,7 +766,8 @@ static int lm_merge(const LatentAttnParams& p, int ntiles, int nchunk, cudaStrea
 
 template <int KVR, int ROT, bool KSPLIT>
 static int lm_launch_as(const LatentAttnParams& p, int ntiles, cudaStream_t st) {
-    const size_t smem = (size_t)((KSPLIT ? 16 : kLmRows) + 2 * kLmKeys) * (KVR + ROT + kLmPad) * sizeof(bf16_t);
+    const size_t smem = ((size_t)((KSPLIT ? 16 : kLmRows) + 2 * kLmKeys) * (KVR + ROT + kLmPad) + (KSPLIT ? 0 : 4 * 16 * kLmKeys)) *
+                        sizeof(bf16_t);
     if (smem > (size_t)device_info().max_smem_optin) return PA_ERR_UNSUPPORTED;
     const bool exact = p.kv_rank == KVR && p.rot_dim == ROT;
     auto kern = exact ? latent_attention_mma_kernel<KVR, ROT, KSPLIT, true> : latent_attention_mma_kernel<KVR, ROT, KSPLIT, false>;
